@@ -1,0 +1,65 @@
+"""ctypes binding of libdmm.so: one Python function per entry point of include/dmm.h."""
+from __future__ import annotations
+
+import ctypes
+import os
+
+from . import build as _build
+
+_LIB = None
+
+# mirrors of the constants in include/dmm.h
+SIGN_SLOW, SIGN_FAST = 0, 1
+LAYOUT_TILE, LAYOUT_FAST = 0, 1
+PATH_AUTO, PATH_GEMV, PATH_TCGEN05 = 0, 1, 2
+FLAG_ACCUMULATE, FLAG_PDL = 1, 2
+STATUS_WAIT_TIMEOUT, STATUS_BAD_CODEBOOK, STATUS_BAD_SMEM = 1, 2, 4
+
+EXPORTS = (
+    "dmm_i8", "dmm_f16", "dmm_decode", "dmm_workspace_bytes", "dmm_status", "dmm_select_path",
+    "dmm_launch_count", "dmm_error_string", "dmm_version",
+)
+
+
+def lib() -> ctypes.CDLL:
+    """Loads the CUDA library, compiling it first when it is missing or stale and nvcc is at
+    hand.  There is no fallback: without the library every operator raises."""
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    path = _build.LIB
+    try:
+        path = _build.build()
+    except Exception:
+        if not os.path.exists(path):
+            raise
+    L = ctypes.CDLL(path)
+    vp, i64, ci, cu, sz = ctypes.c_void_p, ctypes.c_int64, ctypes.c_int, ctypes.c_uint, ctypes.c_size_t
+    L.dmm_i8.argtypes = [vp, vp, vp, vp, i64, i64, i64, ci, ci, cu, vp, sz, vp]
+    L.dmm_i8.restype = ci
+    L.dmm_f16.argtypes = [vp, vp, vp, ctypes.c_float, vp, i64, i64, i64, ci, ci, ci, cu, vp, sz, vp]
+    L.dmm_f16.restype = ci
+    L.dmm_decode.argtypes = [vp, vp, ci, vp, i64, i64, ci, ci, vp]
+    L.dmm_decode.restype = ci
+    L.dmm_workspace_bytes.argtypes = [i64, i64, i64]
+    L.dmm_workspace_bytes.restype = sz
+    L.dmm_status.argtypes = [ctypes.POINTER(cu)]
+    L.dmm_status.restype = ci
+    L.dmm_select_path.argtypes = [i64, i64, i64]
+    L.dmm_select_path.restype = ci
+    L.dmm_launch_count.argtypes = []
+    L.dmm_launch_count.restype = ctypes.c_uint64
+    L.dmm_error_string.argtypes = [ci]
+    L.dmm_error_string.restype = ctypes.c_char_p
+    L.dmm_version.argtypes = []
+    L.dmm_version.restype = ctypes.c_char_p
+    _LIB = L
+    return L
+
+
+def check(rc: int, what: str) -> None:
+    """Turns a non-zero return value into RuntimeError, as TORCH_CHECK does in the
+    reference's host wrappers (decode_matmul_cuda.cu:186-207)."""
+    if rc != 0:
+        msg = lib().dmm_error_string(rc).decode()
+        raise RuntimeError(f"{what}: {msg} (code {rc})")

@@ -1,0 +1,224 @@
+// C ABI of libdmm (declared in include/dmm.h): argument validation, workspace and
+// per-device state, path selection, kernel launches.  The whole library is this one
+// translation unit; the kernel headers are included below.
+#include <atomic>
+#include <mutex>
+
+#include "dmm_common.cuh"
+#include "dmm_decode.cuh"
+#include "dmm_launch.h"
+#include "dmm_stream.cuh"
+
+namespace dmm {
+
+constexpr int kMaxDevices = 64;
+
+struct DeviceState {
+    int num_sms = 0;
+    void *workspace = nullptr;  // library-owned default workspace
+    size_t workspace_bytes = 0;
+};
+
+static std::mutex g_mutex;
+static DeviceState g_dev[kMaxDevices];
+static std::atomic<uint64_t> g_launches{0};
+
+static int current_device_state(DeviceState **out) {
+    int dev = 0;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess) return err;
+    if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+    std::lock_guard<std::mutex> lock(g_mutex);
+    DeviceState &d = g_dev[dev];
+    if (d.num_sms == 0) {
+        err = cudaDeviceGetAttribute(&d.num_sms, cudaDevAttrMultiProcessorCount, dev);
+        if (err != cudaSuccess) return err;
+    }
+    *out = &d;
+    return 0;
+}
+
+static size_t ticket_bytes(long long N) {
+    const size_t b = static_cast<size_t>(N / 16) * sizeof(unsigned);
+    return (b + 255) & ~static_cast<size_t>(255);
+}
+
+static size_t workspace_need(long long N, int num_sms) {
+    return ticket_bytes(N) + static_cast<size_t>(num_sms) * 2 * kPartialValues * 4;
+}
+
+// Returns the workspace to use: the caller's (checked for size) or the library's own,
+// grown on demand.  The ticket counters must be zero before the first launch; the
+// library's buffer is cleared when it is (re)allocated, a caller's buffer by the caller.
+static int resolve_workspace(DeviceState *d, long long N, void *user, size_t user_bytes, cudaStream_t stream,
+                             void **ws) {
+    const size_t need = workspace_need(N, d->num_sms);
+    if (user != nullptr) {
+        if (user_bytes < need) return DMM_ERR_WORKSPACE;
+        if (reinterpret_cast<uintptr_t>(user) % 256 != 0) return DMM_ERR_ALIGN;
+        *ws = user;
+        return 0;
+    }
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (d->workspace_bytes < need) {
+        // Work already enqueued may still use the old buffer: drain before replacing it.
+        cudaError_t err = cudaDeviceSynchronize();
+        if (err != cudaSuccess) return err;
+        if (d->workspace) cudaFree(d->workspace);
+        d->workspace = nullptr;
+        d->workspace_bytes = 0;
+        const size_t bytes = need < (size_t(8) << 20) ? (size_t(8) << 20) : need;
+        err = cudaMalloc(&d->workspace, bytes);
+        if (err != cudaSuccess) return err;
+        err = cudaMemset(d->workspace, 0, bytes);
+        if (err != cudaSuccess) return err;
+        d->workspace_bytes = bytes;
+    }
+    (void)stream;
+    *ws = d->workspace;
+    return 0;
+}
+
+static bool aligned16(const void *p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; }
+
+static int check_common(const void *x, const void *codes, const void *cb, const void *out, long long M, long long N,
+                        long long K, int sign_convention, int layout) {
+    if (!x || !codes || !cb || !out) return DMM_ERR_NULL;
+    if (M < 1 || N < 16 || K < 32 || N % 16 != 0 || K % 32 != 0) return DMM_ERR_SHAPE;
+    if (M > (1ll << 20) || N > (1ll << 24) || K > (1ll << 17)) return DMM_ERR_SHAPE;
+    if (sign_convention != DMM_SIGN_SLOW && sign_convention != DMM_SIGN_FAST) return DMM_ERR_ARG;
+    if (layout != DMM_LAYOUT_TILE && layout != DMM_LAYOUT_FAST) return DMM_ERR_ARG;
+    if (!aligned16(x) || !aligned16(codes) || !aligned16(cb) || !aligned16(out)) return DMM_ERR_ALIGN;
+    return 0;
+}
+
+// Streams the weights once per chunk of 16 batch columns.
+static int run_stream(int family, const void *x, const void *codes, const void *cb, int cb_is_f16, float scale,
+                      void *out, long long M, long long N, long long K, int sign_convention, unsigned flags,
+                      void *workspace, size_t workspace_bytes, cudaStream_t stream) {
+    DeviceState *d = nullptr;
+    int rc = current_device_state(&d);
+    if (rc) return rc;
+    void *ws = nullptr;
+    rc = resolve_workspace(d, N, workspace, workspace_bytes, stream, &ws);
+    if (rc) return rc;
+    const size_t x_elem = family == 0 ? 1 : 2;
+    for (long long m0 = 0; m0 < M; m0 += 16) {
+        StreamParams p = {};
+        p.x = reinterpret_cast<const uint8_t *>(x) + static_cast<size_t>(m0) * K * x_elem;
+        p.codes = codes;
+        p.cb = cb;
+        p.out = reinterpret_cast<uint8_t *>(out) + static_cast<size_t>(m0) * N * 4;
+        p.tickets = reinterpret_cast<unsigned *>(ws);
+        p.partials = reinterpret_cast<uint8_t *>(ws) + ticket_bytes(N);
+        p.M = M - m0 < 16 ? M - m0 : 16;
+        p.N = N;
+        p.K = K;
+        p.scale = scale;
+        p.accumulate = (flags & DMM_FLAG_ACCUMULATE) ? 1 : 0;
+        p.sign_convention = sign_convention;
+        p.cb_is_f16 = cb_is_f16;
+        rc = launch_stream(family, p, d->num_sms, (flags & DMM_FLAG_PDL) != 0, stream);
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+        if (rc) return rc;
+    }
+    return 0;
+}
+
+}  // namespace dmm
+
+using namespace dmm;
+
+extern "C" {
+
+int dmm_i8(const int8_t *x, const int16_t *codes, const int64_t *cb64, int32_t *out, int64_t M, int64_t N, int64_t K,
+           int sign_convention, int layout, unsigned flags, void *workspace, size_t workspace_bytes, void *stream) {
+    int rc = check_common(x, codes, cb64, out, M, N, K, sign_convention, layout);
+    if (rc) return rc;
+    if (layout != DMM_LAYOUT_TILE) return DMM_ERR_UNSUPPORTED;
+    return run_stream(0, x, codes, cb64, 0, 1.0f, out, M, N, K, sign_convention, flags, workspace, workspace_bytes,
+                      static_cast<cudaStream_t>(stream));
+}
+
+int dmm_f16(const void *x, const int16_t *codes, const void *cb16, float scale, float *out, int64_t M, int64_t N,
+            int64_t K, int sign_convention, int layout, int path, unsigned flags, void *workspace,
+            size_t workspace_bytes, void *stream) {
+    int rc = check_common(x, codes, cb16, out, M, N, K, sign_convention, layout);
+    if (rc) return rc;
+    if (path != DMM_PATH_AUTO && path != DMM_PATH_GEMV && path != DMM_PATH_TCGEN05) return DMM_ERR_ARG;
+    if (layout != DMM_LAYOUT_TILE) return DMM_ERR_UNSUPPORTED;
+    if (path == DMM_PATH_AUTO) path = dmm_select_path(M, N, K);
+    if (path == DMM_PATH_TCGEN05) return DMM_ERR_UNSUPPORTED;
+    // the kernels accumulate quarter units: fold the 1/4 into the scale
+    return run_stream(1, x, codes, cb16, 1, 0.25f * scale, out, M, N, K, sign_convention, flags, workspace,
+                      workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+int dmm_decode(const int16_t *codes, const void *cb, int cb_is_f16, void *W_out, int64_t N, int64_t K,
+               int sign_convention, int layout, void *stream) {
+    if (!codes || !cb || !W_out) return DMM_ERR_NULL;
+    if (N < 16 || K < 32 || N % 16 != 0 || K % 32 != 0) return DMM_ERR_SHAPE;
+    if (sign_convention != DMM_SIGN_SLOW && sign_convention != DMM_SIGN_FAST) return DMM_ERR_ARG;
+    if (layout != DMM_LAYOUT_TILE && layout != DMM_LAYOUT_FAST) return DMM_ERR_ARG;
+    if (!aligned16(codes) || !aligned16(cb) || !aligned16(W_out)) return DMM_ERR_ALIGN;
+    if (layout != DMM_LAYOUT_TILE) return DMM_ERR_UNSUPPORTED;
+    DeviceState *d = nullptr;
+    int rc = current_device_state(&d);
+    if (rc) return rc;
+    rc = launch_decode(codes, cb, cb_is_f16 ? 1 : 0, W_out, N, K, sign_convention, d->num_sms,
+                       static_cast<cudaStream_t>(stream));
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return rc;
+}
+
+size_t dmm_workspace_bytes(int64_t M, int64_t N, int64_t K) {
+    (void)M;
+    (void)K;
+    if (N < 16) return 0;
+    DeviceState *d = nullptr;
+    int sms = 256;
+    if (current_device_state(&d) == 0 && d->num_sms > 0) sms = d->num_sms;
+    return workspace_need(N, sms);
+}
+
+int dmm_status(unsigned *status_out) {
+    if (!status_out) return DMM_ERR_NULL;
+    cudaError_t err = cudaDeviceSynchronize();
+    if (err != cudaSuccess) return err;
+    unsigned v = 0;
+    err = cudaMemcpyFromSymbol(&v, g_status, sizeof(v));
+    if (err != cudaSuccess) return err;
+    const unsigned zero = 0;
+    err = cudaMemcpyToSymbol(g_status, &zero, sizeof(zero));
+    if (err != cudaSuccess) return err;
+    *status_out = v;
+    return 0;
+}
+
+int dmm_select_path(int64_t M, int64_t N, int64_t K) {
+    (void)N;
+    (void)K;
+    (void)M;
+    return DMM_PATH_GEMV;
+}
+
+uint64_t dmm_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+const char *dmm_error_string(int code) {
+    switch (code) {
+        case DMM_OK: return "ok";
+        case DMM_ERR_NULL: return "a required pointer is NULL";
+        case DMM_ERR_SHAPE: return "bad shape: need M >= 1, N % 16 == 0, K % 32 == 0";
+        case DMM_ERR_ALIGN: return "a pointer is not 16-byte aligned";
+        case DMM_ERR_ARG: return "unknown enum value";
+        case DMM_ERR_WORKSPACE: return "workspace too small (see dmm_workspace_bytes)";
+        case DMM_ERR_UNSUPPORTED: return "shape or layout not implemented by the chosen path";
+        default: break;
+    }
+    if (code > 0) return cudaGetErrorString(static_cast<cudaError_t>(code));
+    return "unknown error";
+}
+
+const char *dmm_version(void) { return "0.1"; }
+
+}  // extern "C"

@@ -1,0 +1,87 @@
+// Decode-only kernel: tiled codes -> logical [N, K] weights, through the same table and
+// XOR decode core that the matmul kernels use, so a bit-exact check of its output is a
+// check of the decode stage itself.
+#pragma once
+#include "dmm_common.cuh"
+#include "dmm_launch.h"
+
+namespace dmm {
+
+constexpr int kDecodeThreads = 512;
+
+// One thread per 32-bit word of the tile layout (two codes: strip rows g and g+8).
+template <bool kF16>
+__global__ void __launch_bounds__(kDecodeThreads) decode_kernel(const uint32_t *__restrict__ words,
+                                                               const void *__restrict__ cb, int cb_is_f16,
+                                                               void *__restrict__ w_out, long long N, long long K,
+                                                               int sign_convention, unsigned dyn_smem_bytes) {
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    const uint32_t base = smem_u32(smem_raw);
+    const uint32_t lut_addr = (base + 0xFFFFu) & ~0xFFFFu;
+    if (lut_addr + kLutBytes > base + dyn_smem_bytes) {
+        if (threadIdx.x == 0) raise_status(DMM_STATUS_BAD_SMEM);
+        return;
+    }
+    const bool bad = lut_fill(lut_addr, cb, cb_is_f16, sign_convention, kF16 ? 0x80u : 0x00u, threadIdx.x,
+                              kDecodeThreads);
+    if (bad) raise_status(DMM_STATUS_BAD_CODEBOOK);
+    __syncthreads();
+    const LutLane ll = lut_lane(lut_addr, threadIdx.x & 31);
+
+    const long long KT = K / 32;
+    const long long total = N * K / 16;  // words
+    for (long long wi = blockIdx.x * static_cast<long long>(kDecodeThreads) + threadIdx.x; wi < total;
+         wi += static_cast<long long>(gridDim.x) * kDecodeThreads) {
+        const long long strip = wi / (KT * 32);
+        const long long rem = wi - strip * KT * 32;
+        const long long kt = rem >> 5;
+        const int l = static_cast<int>(rem & 31), g = l >> 2, t = l & 3;
+        const uint32_t word = __ldg(words + wi);
+        const uint2 d0 = decode8<0>(word, ll), d1 = decode8<1>(word, ll);
+        const long long n0 = strip * 16 + g, k0 = 32 * kt + 8 * t;
+        if constexpr (kF16) {
+            uint32_t a[4], b[4];
+            bytes_to_half2(d0, a);
+            bytes_to_half2(d1, b);
+            const __half2 quarter = __float2half2_rn(0.25f);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                __half2 ha = __hmul2(*reinterpret_cast<__half2 *>(&a[i]), quarter);
+                __half2 hb = __hmul2(*reinterpret_cast<__half2 *>(&b[i]), quarter);
+                a[i] = *reinterpret_cast<uint32_t *>(&ha);
+                b[i] = *reinterpret_cast<uint32_t *>(&hb);
+            }
+            __half *w = reinterpret_cast<__half *>(w_out);
+            *reinterpret_cast<uint4 *>(w + n0 * K + k0) = make_uint4(a[0], a[1], a[2], a[3]);
+            *reinterpret_cast<uint4 *>(w + (n0 + 8) * K + k0) = make_uint4(b[0], b[1], b[2], b[3]);
+        } else {
+            int8_t *w = reinterpret_cast<int8_t *>(w_out);
+            *reinterpret_cast<uint2 *>(w + n0 * K + k0) = d0;
+            *reinterpret_cast<uint2 *>(w + (n0 + 8) * K + k0) = d1;
+        }
+    }
+}
+
+inline int launch_decode(const void *codes, const void *cb, int cb_is_f16, void *w_out, long long N, long long K,
+                         int sign_convention, int num_sms, cudaStream_t stream) {
+    constexpr unsigned kDyn = 0xFFFFu + kLutBytes + 1;
+    const long long total = N * K / 16;
+    long long blocks = (total + kDecodeThreads - 1) / kDecodeThreads;
+    if (blocks > num_sms) blocks = num_sms;
+    if (blocks < 1) blocks = 1;
+    cudaError_t err;
+    if (cb_is_f16) {
+        err = cudaFuncSetAttribute(decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDyn);
+        if (err != cudaSuccess) return err;
+        decode_kernel<true><<<(unsigned)blocks, kDecodeThreads, kDyn, stream>>>(
+            reinterpret_cast<const uint32_t *>(codes), cb, 1, w_out, N, K, sign_convention, kDyn);
+    } else {
+        err = cudaFuncSetAttribute(decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDyn);
+        if (err != cudaSuccess) return err;
+        decode_kernel<false><<<(unsigned)blocks, kDecodeThreads, kDyn, stream>>>(
+            reinterpret_cast<const uint32_t *>(codes), cb, 0, w_out, N, K, sign_convention, kDyn);
+    }
+    return cudaGetLastError();
+}
+
+}  // namespace dmm

@@ -1,0 +1,122 @@
+"""PyTorch-facing operators over the C ABI of libdmm.
+
+PyTorch is used for device memory and streams only: every function checks its tensors,
+takes raw pointers and the current CUDA stream, and calls one entry point of
+include/dmm.h.  Nothing here computes on the CPU and nothing synchronises the device.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+
+
+def _req(cond: bool, msg: str) -> None:
+    if not cond:
+        raise RuntimeError(msg)
+
+
+def _check_input(t: torch.Tensor, name: str, dtype: torch.dtype) -> None:
+    # same checks as CHECK_INPUT / TORCH_CHECK(scalar_type) in decode_matmul_cuda.cu:16-18,186-188
+    _req(isinstance(t, torch.Tensor), f"{name} must be a tensor")
+    _req(t.is_cuda, f"{name} must be a CUDA tensor")
+    _req(t.is_contiguous(), f"{name} must be contiguous")
+    _req(t.dtype == dtype, f"{name} must have dtype {dtype}")
+
+
+def _stream_ptr(device) -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+
+
+def _ptr(t: torch.Tensor) -> ctypes.c_void_p:
+    return ctypes.c_void_p(t.data_ptr())
+
+
+def decode_matmul_i8(x, weights_compressed, codebook_abs, output=None, *, sign_convention=_lib.SIGN_SLOW,
+                     layout=_lib.LAYOUT_TILE, accumulate=False, pdl=False):
+    """int32 [M, N] = x (int8 [M, K]) . decode(codes)^T, exact.
+
+    ``weights_compressed`` is int16 [N, K/8] in the given layout, ``codebook_abs`` int64[256].
+    With ``output`` given the result is written (or, with ``accumulate``, added) in place and
+    the same tensor is returned; otherwise a new tensor is returned
+    (decode_matmul_cuda.cu:178-234, fast_decode_matmul_cuda.cu:137-184)."""
+    _check_input(x, "x", torch.int8)
+    _check_input(weights_compressed, "weights_compressed", torch.int16)
+    _check_input(codebook_abs, "codebook_abs", torch.int64)
+    _req(x.dim() == 2 and weights_compressed.dim() == 2, "x and weights_compressed must be 2-D")
+    _req(codebook_abs.numel() == 256, "codebook_abs must have 256 entries")
+    _req(x.size(-1) == weights_compressed.size(-1) << 3, "x.size(-1) must equal 8 * weights_compressed.size(-1)")
+    M, K = x.shape
+    N = weights_compressed.size(0)
+    with torch.cuda.device(x.device):
+        if output is None:
+            _req(not accumulate, "accumulate needs an output tensor")
+            output = torch.empty((M, N), dtype=torch.int32, device=x.device)
+        else:
+            _check_input(output, "output", torch.int32)
+            _req(tuple(output.shape) == (M, N), "output must have shape [M, N]")
+        flags = (_lib.FLAG_ACCUMULATE if accumulate else 0) | (_lib.FLAG_PDL if pdl else 0)
+        rc = _lib.lib().dmm_i8(_ptr(x), _ptr(weights_compressed), _ptr(codebook_abs), _ptr(output), M, N, K,
+                               sign_convention, layout, flags, None, 0, _stream_ptr(x.device))
+    _lib.check(rc, "decode_matmul")
+    return output
+
+
+def decode_matmul_fp16(x, weights_compressed, codebook_fp16, scale=1.0, output=None, *,
+                       sign_convention=_lib.SIGN_SLOW, layout=_lib.LAYOUT_TILE, path=_lib.PATH_AUTO,
+                       accumulate=False, pdl=False):
+    """fp32 [M, N] = scale * x (fp16 [M, K]) . W^T with W = decode(codes) / 4, fp32 accumulation.
+    ``codebook_fp16`` is fp16 [256, 8] whose entries are odd multiples of 1/2."""
+    _check_input(x, "x", torch.float16)
+    _check_input(weights_compressed, "weights_compressed", torch.int16)
+    _check_input(codebook_fp16, "codebook_fp16", torch.float16)
+    _req(x.dim() == 2 and weights_compressed.dim() == 2, "x and weights_compressed must be 2-D")
+    _req(tuple(codebook_fp16.shape) == (256, 8), "codebook_fp16 must have shape [256, 8]")
+    _req(x.size(-1) == weights_compressed.size(-1) << 3, "x.size(-1) must equal 8 * weights_compressed.size(-1)")
+    M, K = x.shape
+    N = weights_compressed.size(0)
+    with torch.cuda.device(x.device):
+        if output is None:
+            _req(not accumulate, "accumulate needs an output tensor")
+            output = torch.empty((M, N), dtype=torch.float32, device=x.device)
+        else:
+            _check_input(output, "output", torch.float32)
+            _req(tuple(output.shape) == (M, N), "output must have shape [M, N]")
+        flags = (_lib.FLAG_ACCUMULATE if accumulate else 0) | (_lib.FLAG_PDL if pdl else 0)
+        rc = _lib.lib().dmm_f16(_ptr(x), _ptr(weights_compressed), _ptr(codebook_fp16), float(scale), _ptr(output),
+                                M, N, K, sign_convention, layout, path, flags, None, 0, _stream_ptr(x.device))
+    _lib.check(rc, "decode_matmul_fp16")
+    return output
+
+
+def decode_weights(weights_compressed, codebook, *, sign_convention=_lib.SIGN_SLOW, layout=_lib.LAYOUT_TILE):
+    """Decoded weights in logical order: int8 [N, K] (= 4 * weight) for an int64 codebook,
+    fp16 [N, K] for an fp16 codebook."""
+    _check_input(weights_compressed, "weights_compressed", torch.int16)
+    _req(weights_compressed.dim() == 2, "weights_compressed must be 2-D")
+    is_f16 = codebook.dtype == torch.float16
+    _check_input(codebook, "codebook", torch.float16 if is_f16 else torch.int64)
+    _req(codebook.numel() == (2048 if is_f16 else 256), "codebook must have 256 entries")
+    N, K8 = weights_compressed.shape
+    with torch.cuda.device(weights_compressed.device):
+        out = torch.empty((N, K8 * 8), dtype=torch.float16 if is_f16 else torch.int8,
+                          device=weights_compressed.device)
+        rc = _lib.lib().dmm_decode(_ptr(weights_compressed), _ptr(codebook), int(is_f16), _ptr(out), N, K8 * 8,
+                                   sign_convention, layout, _stream_ptr(out.device))
+    _lib.check(rc, "decode_weights")
+    return out
+
+
+def status(device=None) -> int:
+    """Reads and clears the device status word (synchronises): 0 when every kernel since the
+    last call finished its bounded waits and accepted its codebook."""
+    v = ctypes.c_uint(0)
+    with torch.cuda.device(device if device is not None else torch.cuda.current_device()):
+        _lib.check(_lib.lib().dmm_status(ctypes.byref(v)), "dmm_status")
+    return v.value
+
+
+def launch_count() -> int:
+    return int(_lib.lib().dmm_launch_count())

@@ -1,0 +1,122 @@
+/*
+ * dmm.h -- C ABI of libdmm, the B200 (sm_100a) codebook decode-and-matmul library.
+ *
+ * Every entry point takes plain device pointers and sizes, enqueues its work on the
+ * given CUDA stream and returns immediately: it never synchronises the device, never
+ * throws and never exits the process.  Return value: 0 = enqueued, negative = argument
+ * error (DMM_ERR_*), positive = the cudaError_t of a failed runtime call.
+ *
+ * Data formats (shared by all entry points)
+ *   code word      uint16: bits 0..7 codebook index, bits 8..14 seven stored sign bits,
+ *                  bit 15 shift bit; the eighth sign is the parity of the seven.
+ *   codes_tiled    int16, N*K/8 values in the tile layout of the reference's
+ *                  transpose_tile() (test_decode_matmul.py:101-109):
+ *                  [N/16][K/32][g:8][t:4][h:2], row n = 16*nt + 8*h + g, column j = 4*kt + t.
+ *   cb64           int64[256]; byte i of entry e is int8(4 * codebook value i)
+ *                  (test_decode_matmul.py:85).
+ *   cb16           fp16[256][8]; the same table as real values (byte / 4).
+ *   sign convention DMM_SIGN_SLOW: stored bit i -> weight i (i<7), parity -> weight 7
+ *                  (decode_matmul_cuda.cu:50-53); DMM_SIGN_FAST: parity -> weight 0,
+ *                  stored bit i -> weight i+1 (fast_decode_matmul_cuda.cu:52-53).
+ * The fast kernels need every codebook byte to be congruent to 2 modulo 4 (true of the
+ * E8P table and of tables drawn from {0.5,1.5,2.5,3.5}); the same assumption is built into
+ * the reference's decode8weights.  A table that breaks it raises DMM_STATUS_BAD_CODEBOOK in
+ * the device status word and the output of that call is undefined.
+ */
+#ifndef DMM_H_
+#define DMM_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DMM_OK 0
+#define DMM_ERR_NULL (-1)        /* a required pointer is NULL */
+#define DMM_ERR_SHAPE (-2)       /* M < 1, N % 16 != 0, K % 32 != 0, or a size out of range */
+#define DMM_ERR_ALIGN (-3)       /* a pointer is not 16-byte aligned */
+#define DMM_ERR_ARG (-4)         /* unknown enum value */
+#define DMM_ERR_WORKSPACE (-5)   /* caller-supplied workspace too small */
+#define DMM_ERR_UNSUPPORTED (-6) /* shape outside what the chosen path implements */
+
+#define DMM_SIGN_SLOW 0
+#define DMM_SIGN_FAST 1
+
+#define DMM_LAYOUT_TILE 0 /* transpose_tile() layout, used by decode_matmul_cuda */
+#define DMM_LAYOUT_FAST 1 /* uint32 [N/32][K/16][32] layout, used by fast_decode_matmul_cuda */
+
+#define DMM_PATH_AUTO 0
+#define DMM_PATH_GEMV 1    /* CUDA-core/legacy-MMA streaming path, any M */
+#define DMM_PATH_TCGEN05 2 /* tcgen05 + TMEM path, M >= 16 */
+
+/* launch flags (bit mask) */
+#define DMM_FLAG_ACCUMULATE 1u /* out += result instead of out = result */
+#define DMM_FLAG_PDL 2u        /* launch with programmatic stream serialization: the kernel's
+                                  weight prefetch may overlap the tail of the previous kernel
+                                  in the stream; activations are read only after it finished */
+
+/* bits of the device status word */
+#define DMM_STATUS_WAIT_TIMEOUT 1u /* a bounded device-side wait expired */
+#define DMM_STATUS_BAD_CODEBOOK 2u /* codebook byte not congruent to 2 mod 4, or fp16 entry not k/4 */
+#define DMM_STATUS_BAD_SMEM 4u     /* shared-memory carve-up did not fit */
+
+/*
+ * Integer family.  out[M,N] (int32) (+)= x[M,K] (int8) . decode(codes)[N,K]^T, exact.
+ * Replaces the kernel and host wrapper of decode_matmul_cuda/decode_matmul_cuda.cu:68-234
+ * (3-argument form: flags = 0) and of decode_matmul_cuda/fast_decode_matmul_cuda.cu:70-184
+ * (4-argument, in-place accumulate form: flags = DMM_FLAG_ACCUMULATE, DMM_SIGN_FAST,
+ * DMM_LAYOUT_FAST).  Accepts every M >= 1, N % 16 == 0 (N % 32 for the fast layout),
+ * K % 32 == 0; the reference's extra limits (M % 8, K % 2048, K >= 4096) are gone.
+ * workspace may be NULL: the library then uses a per-device buffer it allocates on first
+ * use; calls that can overlap on the GPU must pass distinct workspaces.
+ */
+int dmm_i8(const int8_t *x, const int16_t *codes, const int64_t *cb64, int32_t *out,
+           int64_t M, int64_t N, int64_t K, int sign_convention, int layout, unsigned flags,
+           void *workspace, size_t workspace_bytes, void *stream);
+
+/*
+ * fp16 family.  out[M,N] (fp32) (+)= scale * x[M,K] (fp16) . W[N,K]^T with
+ * W = decode(codes)/4, fp32 accumulation.  The reference has no fp16 path; semantics are
+ * its integer decode (test_decode_matmul.py:29-55) read as quarter units.
+ * cb16 is fp16[256][8].  path: DMM_PATH_*.
+ */
+int dmm_f16(const void *x, const int16_t *codes, const void *cb16, float scale, float *out,
+            int64_t M, int64_t N, int64_t K, int sign_convention, int layout, int path,
+            unsigned flags, void *workspace, size_t workspace_bytes, void *stream);
+
+/*
+ * Decode only.  W_out[N,K] in logical (row-major) order: int8 (= 4 * weight) when
+ * cb_is_f16 == 0 and cb is cb64, fp16 (= weight) when cb_is_f16 != 0 and cb is cb16.
+ * Exposes decode8weights (decode_matmul_cuda.cu:45-65 / fast_decode_matmul_cuda.cu:46-67)
+ * so that the decoded weights can be compared bit for bit.
+ */
+int dmm_decode(const int16_t *codes, const void *cb, int cb_is_f16, void *W_out, int64_t N,
+               int64_t K, int sign_convention, int layout, void *stream);
+
+/* Bytes of workspace a call of dmm_i8 / dmm_f16 with these sizes needs (0 if none). */
+size_t dmm_workspace_bytes(int64_t M, int64_t N, int64_t K);
+
+/*
+ * Reads and clears the status word of the current device (synchronises the device).
+ * Replaces the reference's gpuAssert -> exit() (decode_matmul_cuda.cu:35-42).
+ */
+int dmm_status(unsigned *status_out);
+
+/* Which path DMM_PATH_AUTO resolves to for this shape (DMM_PATH_GEMV or DMM_PATH_TCGEN05). */
+int dmm_select_path(int64_t M, int64_t N, int64_t K);
+
+/* Number of kernels the library has launched in this process (all devices, all entry points). */
+uint64_t dmm_launch_count(void);
+
+/* Human-readable text for a return value of this API. */
+const char *dmm_error_string(int code);
+
+/* Library version, "major.minor". */
+const char *dmm_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DMM_H_ */

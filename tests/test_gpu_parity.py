@@ -1,0 +1,186 @@
+"""Parity of the CUDA path (through the C ABI) with the CPU oracle.  Needs a B200."""
+import numpy as np
+import pytest
+import torch
+
+import decode_matmul_b200 as dmm
+from oracle import dmm_oracle as o
+
+pytestmark = pytest.mark.gpu
+
+MAX_ABS_ERR = 1e-2  # fp16 family, against the float64-accumulated oracle
+REL_L2 = 1e-3
+
+
+def _dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def _codes(rng, n, k):
+    return rng.integers(-32768, 32768, size=(n, k // 8)).astype(np.int16)
+
+
+@pytest.fixture(scope="module")
+def e8p(golden):
+    return np.ascontiguousarray(golden["e8p_codebook"]["codebook_abs"])
+
+
+@pytest.fixture(autouse=True)
+def _status_clean():
+    yield
+    assert dmm.status() == 0, "a kernel raised the device status word"
+
+
+def test_decode_all_code_words_bit_exact(golden, e8p):
+    """Every code word once, through the decode core the matmul kernels use."""
+    codes = np.arange(65536, dtype=np.uint16).view(np.int16).reshape(256, 256)
+    tiled = _dev(o.tile_pack(codes))
+    w = dmm.decode_weights(tiled, _dev(e8p)).cpu().numpy()
+    want = golden["decode_all_codes"]["table"][codes.view(np.uint16).astype(np.int64)].reshape(256, 2048)
+    assert np.array_equal(w, want)
+    w_fast = dmm.decode_weights(tiled, _dev(e8p), sign_convention=dmm.SIGN_FAST).cpu().numpy()
+    assert np.array_equal(w_fast, o.decode_weights(codes, e8p, o.SIGN_FAST))
+    cb16 = o.cb64_to_cb16(e8p)
+    w16 = dmm.decode_weights(tiled, _dev(cb16)).cpu().numpy()
+    assert w16.dtype == np.float16
+    assert np.array_equal(w16.view(np.uint16), o.decode_weights_f16(codes, cb16).view(np.uint16))
+    syn = o.synthetic_codebook(42)
+    w16 = dmm.decode_weights(tiled, _dev(syn)).cpu().numpy()
+    assert np.array_equal(w16.view(np.uint16), o.decode_weights_f16(codes, syn).view(np.uint16))
+
+
+def test_reference_test_case(golden, e8p):
+    """The reference's own case (8 x 16 x 4096, test_decode_matmul.py:126-138) from the fixture."""
+    r = golden["matmul_ref_shape"]
+    y = dmm.decode_matmul_i8(_dev(r["x"]), _dev(r["tiled"]), _dev(e8p))
+    assert y.dtype == torch.int32 and tuple(y.shape) == (8, 16)
+    assert np.array_equal(y.cpu().numpy(), r["y"])
+
+
+def test_reference_script_flow(e8p):
+    """Same flow as the reference's script: seed 42, CUDA-generated inputs, the drop-in module."""
+    from decode_matmul_cuda import decode_matmul as decode_matmul_cuda
+
+    torch.random.manual_seed(42)
+    device = torch.device("cuda")
+    cb = dmm.build_codebook_abs(device)
+    assert np.array_equal(cb.cpu().numpy(), e8p)
+    M, N, K = 8, 16, 4096
+    x = torch.randint(-128, 128, (M, K), dtype=torch.int8, device=device)
+    w = torch.randint(-32768, 32768, (N, K // 8), dtype=torch.int16, device=device)
+    result = decode_matmul_cuda(x, dmm.transpose_tile(w), cb)
+    want = o.decode_matmul_int(x.cpu().numpy(), w.cpu().numpy(), e8p)
+    assert torch.all(result.cpu() == torch.from_numpy(want)).item()
+
+
+I8_SHAPES = [(8, 16, 32), (1, 16, 4096), (3, 48, 160), (8, 64, 2048), (5, 4096, 4096), (1, 4096, 11008),
+             (8, 11008, 4096), (13, 256, 1024), (16, 512, 512), (33, 128, 256), (2, 8192, 8192)]
+
+
+@pytest.mark.parametrize("M,N,K", I8_SHAPES)
+def test_int_family_exact(M, N, K, e8p):
+    rng = np.random.default_rng(M * 1000003 + N * 101 + K)
+    x = rng.integers(-128, 128, size=(M, K)).astype(np.int8)
+    codes = _codes(rng, N, K)
+    want = o.decode_matmul_int(x, codes, e8p)
+    tiled, cb = _dev(o.tile_pack(codes)), _dev(e8p)
+    for _ in range(2):  # the second call checks that the workspace counters were reset
+        y = dmm.decode_matmul_i8(_dev(x), tiled, cb)
+        assert np.array_equal(y.cpu().numpy(), want)
+
+
+def test_int_family_fast_convention_and_accumulate(e8p):
+    rng = np.random.default_rng(11)
+    M, N, K = 8, 96, 1024
+    x = rng.integers(-128, 128, size=(M, K)).astype(np.int8)
+    codes = _codes(rng, N, K)
+    base = rng.integers(-1000, 1000, size=(M, N)).astype(np.int32)
+    out = _dev(base)
+    y = dmm.decode_matmul_i8(_dev(x), _dev(o.tile_pack(codes)), _dev(e8p), out,
+                             sign_convention=dmm.SIGN_FAST, accumulate=True)
+    assert y.data_ptr() == out.data_ptr()
+    assert np.array_equal(y.cpu().numpy(), base + o.decode_matmul_int(x, codes, e8p, o.SIGN_FAST))
+
+
+def test_int_family_synthetic_codebook_and_extremes():
+    rng = np.random.default_rng(12)
+    cb = o.cb16_to_cb64(o.synthetic_codebook(7))
+    M, N, K = 4, 64, 512
+    x = np.full((M, K), -128, np.int8)
+    x[1] = 127
+    codes = _codes(rng, N, K)
+    codes[0, :] = np.int16(-1)       # 0xFFFF everywhere
+    codes[1, :] = 0
+    codes[2, :] = np.int16(-32768)   # only the shift bit
+    y = dmm.decode_matmul_i8(_dev(x), _dev(o.tile_pack(codes)), _dev(cb))
+    assert np.array_equal(y.cpu().numpy(), o.decode_matmul_int(x, codes, cb))
+
+
+F16_SHAPES = [(1, 16, 32), (1, 4096, 4096), (1, 11008, 4096), (1, 4096, 11008), (2, 48, 160), (4, 4096, 4096),
+              (8, 4096, 11008), (16, 1024, 2048), (1, 8192, 8192), (1, 10240, 8192), (33, 256, 512)]
+
+
+def _check_f16(y, want):
+    err = np.abs(y - want).max()
+    rel = np.linalg.norm(y - want) / max(np.linalg.norm(want), 1e-30)
+    assert err <= MAX_ABS_ERR, f"max abs err {err}"
+    assert rel <= REL_L2, f"rel L2 {rel}"
+
+
+@pytest.mark.parametrize("M,N,K", F16_SHAPES)
+def test_fp16_family(M, N, K):
+    rng = np.random.default_rng(M * 7 + N * 13 + K)
+    cb16 = o.synthetic_codebook(42)
+    x = rng.standard_normal((M, K)).astype(np.float16)
+    codes = _codes(rng, N, K)
+    want = o.decode_matmul_f16(x, codes, cb16, 1.0)
+    tiled, cb = _dev(o.tile_pack(codes)), _dev(cb16)
+    for _ in range(2):
+        y = dmm.decode_matmul_fp16(_dev(x), tiled, cb, 1.0, path=dmm.PATH_GEMV)
+        assert y.dtype == torch.float32
+        _check_f16(y.cpu().numpy(), want)
+
+
+def test_fp16_family_scale_e8p_and_linearity(e8p):
+    rng = np.random.default_rng(21)
+    M, N, K = 2, 512, 4096
+    cb16 = o.cb64_to_cb16(e8p)
+    x = rng.standard_normal((M, K)).astype(np.float16)
+    codes = _codes(rng, N, K)
+    tiled, cb = _dev(o.tile_pack(codes)), _dev(cb16)
+    y = dmm.decode_matmul_fp16(_dev(x), tiled, cb, 0.5).cpu().numpy()
+    _check_f16(y, o.decode_matmul_f16(x, codes, cb16, 0.5))
+    # linearity in the scale and in x (exact powers of two)
+    y2 = dmm.decode_matmul_fp16(_dev((x * np.float16(2)).astype(np.float16)), tiled, cb, 0.25).cpu().numpy()
+    assert np.array_equal(y, y2)
+
+
+def test_bad_codebook_raises_status():
+    cb = np.zeros(256, np.int64)  # bytes 0: not congruent to 2 mod 4
+    rng = np.random.default_rng(1)
+    x = rng.integers(-128, 128, size=(8, 64)).astype(np.int8)
+    dmm.decode_matmul_i8(_dev(x), _dev(o.tile_pack(_codes(rng, 16, 64))), _dev(cb))
+    assert dmm.status() & 2
+    assert dmm.status() == 0
+
+
+def test_errors_raise_runtime_error(e8p):
+    x = torch.zeros((8, 64), dtype=torch.int8, device="cuda")
+    w = torch.zeros((16, 8), dtype=torch.int16, device="cuda")
+    cb = _dev(e8p)
+    with pytest.raises(RuntimeError):
+        dmm.decode_matmul_i8(x, w[:, :4], cb)            # K mismatch
+    with pytest.raises(RuntimeError):
+        dmm.decode_matmul_i8(x.to(torch.int16), w, cb)   # dtype
+    with pytest.raises(RuntimeError):
+        dmm.decode_matmul_i8(x.t(), w, cb)               # not contiguous
+    with pytest.raises(RuntimeError):
+        dmm.decode_matmul_i8(x[:, :48].contiguous(), w[:, :6].contiguous(), cb)  # K % 32
+
+
+def test_launches_are_counted(e8p):
+    before = dmm.launch_count()
+    x = torch.zeros((8, 64), dtype=torch.int8, device="cuda")
+    w = torch.zeros((16, 8), dtype=torch.int16, device="cuda")
+    dmm.decode_matmul_i8(x, w, _dev(e8p))
+    assert dmm.launch_count() == before + 1

@@ -1,0 +1,101 @@
+"""Host-side logic that needs no GPU: packers, codebooks, the C ABI's exports and its
+argument validation (every check returns before any CUDA call)."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+
+import decode_matmul_b200 as dmm
+from decode_matmul_b200 import _lib
+from oracle import dmm_oracle as o
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol():
+    header = open(os.path.join(ROOT, "include", "dmm.h")).read()
+    declared = set(re.findall(r"\b(dmm_[a-z0-9_]+)\s*\(", header))
+    assert declared == set(_lib.EXPORTS)
+    L = _lib.lib()
+    for name in declared:
+        assert getattr(L, name) is not None
+    assert L.dmm_version().decode().count(".") == 1
+
+
+def test_constants_match_header():
+    header = open(os.path.join(ROOT, "include", "dmm.h")).read()
+    vals = {k: int(v.rstrip("u"), 0) for k, v in re.findall(r"#define (DMM_[A-Z0-9_]+) \(?(-?[0-9a-fx]+u?)\)?", header)}
+    assert vals["DMM_SIGN_SLOW"] == _lib.SIGN_SLOW and vals["DMM_SIGN_FAST"] == _lib.SIGN_FAST
+    assert vals["DMM_LAYOUT_TILE"] == _lib.LAYOUT_TILE and vals["DMM_LAYOUT_FAST"] == _lib.LAYOUT_FAST
+    assert (vals["DMM_PATH_AUTO"], vals["DMM_PATH_GEMV"], vals["DMM_PATH_TCGEN05"]) == (0, 1, 2)
+    assert vals["DMM_FLAG_ACCUMULATE"] == _lib.FLAG_ACCUMULATE and vals["DMM_FLAG_PDL"] == _lib.FLAG_PDL
+
+
+def test_argument_errors_are_status_codes_not_crashes():
+    L = _lib.lib()
+    buf = (ctypes.c_char * 4096)()
+    a = ctypes.addressof(buf)
+    a = (a + 255) & ~255
+    p = ctypes.c_void_p(a)
+    assert L.dmm_i8(None, p, p, p, 8, 16, 32, 0, 0, 0, None, 0, None) == -1
+    assert L.dmm_i8(p, p, p, p, 0, 16, 32, 0, 0, 0, None, 0, None) == -2
+    assert L.dmm_i8(p, p, p, p, 8, 24, 32, 0, 0, 0, None, 0, None) == -2
+    assert L.dmm_i8(p, p, p, p, 8, 16, 48, 0, 0, 0, None, 0, None) == -2
+    assert L.dmm_i8(ctypes.c_void_p(a + 4), p, p, p, 8, 16, 32, 0, 0, 0, None, 0, None) == -3
+    assert L.dmm_i8(p, p, p, p, 8, 16, 32, 7, 0, 0, None, 0, None) == -4
+    assert L.dmm_f16(p, p, p, 1.0, p, 8, 16, 32, 0, 0, 9, 0, None, 0, None) == -4
+    assert L.dmm_decode(p, None, 0, p, 16, 32, 0, 0, None) == -1
+    assert L.dmm_status(None) == -1
+    for code in (0, -1, -2, -3, -4, -5, -6):
+        assert len(L.dmm_error_string(code)) > 0
+
+
+def test_python_wrappers_reject_bad_tensors():
+    x = torch.zeros((8, 64), dtype=torch.int8)
+    w = torch.zeros((16, 8), dtype=torch.int16)
+    cb = torch.zeros(256, dtype=torch.int64)
+    with pytest.raises(RuntimeError, match="CUDA tensor"):
+        dmm.decode_matmul_i8(x, w, cb)
+    import decode_matmul_cuda
+    import fast_decode_matmul_cuda
+    with pytest.raises(RuntimeError):
+        decode_matmul_cuda.decode_matmul(x, w, cb)
+    with pytest.raises(RuntimeError):
+        fast_decode_matmul_cuda.decode_matmul(x, w, cb, torch.zeros((8, 16), dtype=torch.int32))
+
+
+def test_transpose_tile_matches_reference(golden):
+    g = golden["transpose_tile"]
+    t = dmm.transpose_tile(torch.from_numpy(g["logical"]))
+    assert np.array_equal(t.numpy(), g["tiled"])
+    assert np.array_equal(dmm.untranspose_tile(t).numpy(), g["logical"])
+    with pytest.raises(RuntimeError):
+        dmm.transpose_tile(torch.zeros((8, 4), dtype=torch.int16))
+
+
+def test_codebooks(golden):
+    cb = dmm.build_codebook_abs("cpu")
+    assert np.array_equal(cb.numpy(), golden["e8p_codebook"]["codebook_abs"])
+    cb16 = dmm.codebook_to_fp16(cb)
+    assert np.array_equal(cb16.numpy(), o.cb64_to_cb16(cb.numpy()))
+    assert torch.equal(dmm.codebook_from_fp16(cb16), cb)
+    syn = dmm.synthetic_codebook(42)
+    assert syn.shape == (256, 8) and syn.dtype == torch.float16
+    assert set(syn.unique().tolist()) == {0.5, 1.5, 2.5, 3.5}
+    with pytest.raises(RuntimeError):
+        dmm.pack_codebook(torch.full((256, 8), 0.3))
+
+
+def test_shards_tile_independently():
+    rng = np.random.default_rng(5)
+    codes = torch.from_numpy(rng.integers(-32768, 32768, size=(64, 32)).astype(np.int16))
+    rows = [dmm.shard_rows(codes, 2, r) for r in range(2)]
+    # a column-parallel shard of the tiled matrix is a contiguous byte range of it
+    whole = dmm.transpose_tile(codes).reshape(-1)
+    for r in range(2):
+        assert torch.equal(dmm.transpose_tile(rows[r]).reshape(-1), whole[r * whole.numel() // 2:(r + 1) * whole.numel() // 2])
+    cols = [dmm.shard_cols(codes, 2, r) for r in range(2)]
+    assert torch.equal(torch.cat(cols, 1), codes)

@@ -11,7 +11,7 @@ _LIB = None
 # mirrors of the constants in include/dmm.h
 SIGN_SLOW, SIGN_FAST = 0, 1
 LAYOUT_TILE, LAYOUT_FAST = 0, 1
-PATH_AUTO, PATH_GEMV, PATH_TCGEN05 = 0, 1, 2
+PATH_AUTO, PATH_GEMV, PATH_TCGEN05, PATH_TCGEN05_F8 = 0, 1, 2, 3
 FLAG_ACCUMULATE, FLAG_PDL = 1, 2
 STATUS_WAIT_TIMEOUT, STATUS_BAD_CODEBOOK, STATUS_BAD_SMEM = 1, 2, 4
 

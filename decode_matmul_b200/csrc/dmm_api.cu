@@ -8,6 +8,7 @@
 #include "dmm_decode.cuh"
 #include "dmm_launch.h"
 #include "dmm_stream.cuh"
+#include "dmm_umma.cuh"
 
 namespace dmm {
 
@@ -43,16 +44,21 @@ static size_t ticket_bytes(long long N) {
     return (b + 255) & ~static_cast<size_t>(255);
 }
 
-static size_t workspace_need(long long N, int num_sms) {
-    return ticket_bytes(N) + static_cast<size_t>(num_sms) * 2 * kPartialValues * 4;
+// Every path shares the ticket block; the partial block is sized for the widest path
+// that a batch of M columns can take (tcgen05, fp16 operands).
+static size_t workspace_need(long long M, long long N, int num_sms) {
+    size_t per_slot = kPartialValues;
+    const size_t umma = static_cast<size_t>(umma_partial_values(M > 64 ? 64 : M, false));
+    if (umma > per_slot) per_slot = umma;
+    return ticket_bytes(N) + static_cast<size_t>(num_sms) * 2 * per_slot * 4;
 }
 
 // Returns the workspace to use: the caller's (checked for size) or the library's own,
 // grown on demand.  The ticket counters must be zero before the first launch; the
 // library's buffer is cleared when it is (re)allocated, a caller's buffer by the caller.
-static int resolve_workspace(DeviceState *d, long long N, void *user, size_t user_bytes, cudaStream_t stream,
-                             void **ws) {
-    const size_t need = workspace_need(N, d->num_sms);
+static int resolve_workspace(DeviceState *d, long long M, long long N, void *user, size_t user_bytes,
+                             cudaStream_t stream, void **ws) {
+    const size_t need = workspace_need(M, N, d->num_sms);
     if (user != nullptr) {
         if (user_bytes < need) return DMM_ERR_WORKSPACE;
         if (reinterpret_cast<uintptr_t>(user) % 256 != 0) return DMM_ERR_ALIGN;
@@ -100,7 +106,7 @@ static int run_stream(int family, const void *x, const void *codes, const void *
     int rc = current_device_state(&d);
     if (rc) return rc;
     void *ws = nullptr;
-    rc = resolve_workspace(d, N, workspace, workspace_bytes, stream, &ws);
+    rc = resolve_workspace(d, M, N, workspace, workspace_bytes, stream, &ws);
     if (rc) return rc;
     const size_t x_elem = family == 0 ? 1 : 2;
     for (long long m0 = 0; m0 < M; m0 += 16) {
@@ -119,6 +125,39 @@ static int run_stream(int family, const void *x, const void *codes, const void *
         p.sign_convention = sign_convention;
         p.cb_is_f16 = cb_is_f16;
         rc = launch_stream(family, p, d->num_sms, (flags & DMM_FLAG_PDL) != 0, stream);
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+        if (rc) return rc;
+    }
+    return 0;
+}
+
+// tcgen05 path: one launch per chunk of 64 batch columns (8 for the fp6/fp8 operand policy).
+static int run_umma(bool f8, const void *x, const void *codes, const void *cb16, float scale, float *out, long long M,
+                    long long N, long long K, int sign_convention, unsigned flags, void *workspace,
+                    size_t workspace_bytes, cudaStream_t stream) {
+    DeviceState *d = nullptr;
+    int rc = current_device_state(&d);
+    if (rc) return rc;
+    void *ws = nullptr;
+    rc = resolve_workspace(d, M, N, workspace, workspace_bytes, stream, &ws);
+    if (rc) return rc;
+    const long long step = f8 ? 8 : 64;
+    for (long long m0 = 0; m0 < M; m0 += step) {
+        UmmaParams p = {};
+        p.x = reinterpret_cast<const uint8_t *>(x) + static_cast<size_t>(m0) * K * 2;
+        p.codes = codes;
+        p.cb = cb16;
+        p.out = out + static_cast<size_t>(m0) * N;
+        p.tickets = reinterpret_cast<unsigned *>(ws);
+        p.partials = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(ws) + ticket_bytes(N));
+        p.M = M - m0 < step ? M - m0 : step;
+        p.N = N;
+        p.K = K;
+        // accumulators hold sum(x * q / 8) (fp6 weights) or sum(x * q) (fp16 weights); weight = q / 4
+        p.scale = f8 ? 2.0f * scale : 0.25f * scale;
+        p.accumulate = (flags & DMM_FLAG_ACCUMULATE) ? 1 : 0;
+        p.sign_convention = sign_convention;
+        rc = launch_umma(f8, p, d->num_sms, (flags & DMM_FLAG_PDL) != 0, stream);
         g_launches.fetch_add(1, std::memory_order_relaxed);
         if (rc) return rc;
     }
@@ -145,10 +184,13 @@ int dmm_f16(const void *x, const int16_t *codes, const void *cb16, float scale, 
             size_t workspace_bytes, void *stream) {
     int rc = check_common(x, codes, cb16, out, M, N, K, sign_convention, layout);
     if (rc) return rc;
-    if (path != DMM_PATH_AUTO && path != DMM_PATH_GEMV && path != DMM_PATH_TCGEN05) return DMM_ERR_ARG;
+    if (path != DMM_PATH_AUTO && path != DMM_PATH_GEMV && path != DMM_PATH_TCGEN05 && path != DMM_PATH_TCGEN05_F8)
+        return DMM_ERR_ARG;
     if (layout != DMM_LAYOUT_TILE) return DMM_ERR_UNSUPPORTED;
     if (path == DMM_PATH_AUTO) path = dmm_select_path(M, N, K);
-    if (path == DMM_PATH_TCGEN05) return DMM_ERR_UNSUPPORTED;
+    if (path == DMM_PATH_TCGEN05 || path == DMM_PATH_TCGEN05_F8)
+        return run_umma(path == DMM_PATH_TCGEN05_F8, x, codes, cb16, scale, out, M, N, K, sign_convention, flags,
+                        workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
     // the kernels accumulate quarter units: fold the 1/4 into the scale
     return run_stream(1, x, codes, cb16, 1, 0.25f * scale, out, M, N, K, sign_convention, flags, workspace,
                       workspace_bytes, static_cast<cudaStream_t>(stream));
@@ -172,13 +214,12 @@ int dmm_decode(const int16_t *codes, const void *cb, int cb_is_f16, void *W_out,
 }
 
 size_t dmm_workspace_bytes(int64_t M, int64_t N, int64_t K) {
-    (void)M;
     (void)K;
     if (N < 16) return 0;
     DeviceState *d = nullptr;
     int sms = 256;
     if (current_device_state(&d) == 0 && d->num_sms > 0) sms = d->num_sms;
-    return workspace_need(N, sms);
+    return workspace_need(M, N, sms);
 }
 
 int dmm_status(unsigned *status_out) {
@@ -198,8 +239,7 @@ int dmm_status(unsigned *status_out) {
 int dmm_select_path(int64_t M, int64_t N, int64_t K) {
     (void)N;
     (void)K;
-    (void)M;
-    return DMM_PATH_GEMV;
+    return M <= 8 ? DMM_PATH_TCGEN05_F8 : DMM_PATH_TCGEN05;
 }
 
 uint64_t dmm_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }

@@ -162,12 +162,21 @@ __device__ __forceinline__ void mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, ui
 // (the identity behind decode8weights, decode_matmul_cuda.cu:58-62), so
 //   decoded = entry[code & 0xFF] ^ mask[code >> 8]
 // with mask byte i = (sign_i ? 0xFC : 0) ^ (shift ? 0x03 : 0x01) ^ extra, where extra is 0
-// for the integer family and 0x80 (offset binary) for the fp16 family.
+// for the integer family and 0x80 (offset binary) for the fp16 family.  A third byte format
+// (sign-magnitude, for fp6 tensor-core operands) obeys the same entry ^ mask rule.
 // ---------------------------------------------------------------------------------------
 constexpr uint32_t kLutBytes = 65536;
 
-// Sign/shift mask for high code byte h (bit 7 = shift, bits 0..6 = stored signs).
-__host__ __device__ inline uint64_t sign_mask(uint32_t h, int convention, uint32_t extra) {
+// Byte formats the table can produce (the XOR of an entry and a mask byte):
+//   kFmtTwos    two's complement int8 q                (integer family, legacy MMA)
+//   kFmtOffset  offset binary q + 128                  (fp16 family: 0x6400|u is the half 1024+u)
+//   kFmtFp6     sign << 5 | |q|, |q| <= 15             (fp6 E2M3 container: the value is q/8,
+//               because E2M3 codes 0..15 are linear: exponent 0 is subnormal m/8, exponent 1 is
+//               (8+m)/8)
+constexpr int kFmtTwos = 0, kFmtOffset = 1, kFmtFp6 = 2;
+
+// Mask bytes for high code byte h (bit 7 = shift, bits 0..6 = stored signs).
+__host__ __device__ inline uint64_t sign_mask(uint32_t h, int convention, int fmt) {
     const uint32_t s7 = h & 0x7Fu;
     uint32_t par = s7;
     par ^= par >> 4;
@@ -175,18 +184,23 @@ __host__ __device__ inline uint64_t sign_mask(uint32_t h, int convention, uint32
     par ^= par >> 1;
     par &= 1u;
     const uint32_t s8 = convention == DMM_SIGN_SLOW ? (s7 | (par << 7)) : ((s7 << 1) | par);
-    const uint64_t add = (h & 0x80u) ? 0x03u : 0x01u;
+    const uint32_t shift = (h >> 7) & 1u;
     uint64_t m = 0;
     for (int i = 0; i < 8; ++i) {
-        uint64_t b = ((s8 >> i) & 1u) ? 0xFCu : 0x00u;
-        b ^= add ^ extra;
+        const uint32_t sg = (s8 >> i) & 1u;
+        uint64_t b;
+        if (fmt == kFmtFp6) {
+            b = (sg << 5) | ((sg ^ shift) << 1);
+        } else {
+            b = (sg ? 0xFCu : 0x00u) ^ (shift ? 0x03u : 0x01u) ^ (fmt == kFmtOffset ? 0x80u : 0x00u);
+        }
         m |= b << (8 * i);
     }
     return m;
 }
 
-// Codebook entry e as packed int8 x 8, from either table format.  Sets *bad when the
-// entry cannot be decoded by XOR (byte not congruent to 2 mod 4, or fp16 value not k/4).
+// Codebook entry e as packed int8 x 8 (= 4 * value), from either table format.  Sets *bad
+// when the entry cannot be decoded by XOR (byte not congruent to 2 mod 4, fp16 value not k/4).
 __device__ inline uint64_t load_entry(const void *cb, int cb_is_f16, int e, bool *bad) {
     uint64_t v;
     if (!cb_is_f16) {
@@ -207,16 +221,31 @@ __device__ inline uint64_t load_entry(const void *cb, int cb_is_f16, int e, bool
     return v;
 }
 
+// Entry bytes in the given format.  kFmtFp6: (neg << 5) | ((|c| | 1) ^ (neg << 1)); XOR with
+// the mask byte gives sign = s ^ neg and magnitude |c| + 1 or |c| - 1.
+__device__ inline uint64_t format_entry(uint64_t v, int fmt, bool *bad) {
+    if (fmt != kFmtFp6) return v;
+    uint64_t r = 0;
+    for (int i = 0; i < 8; ++i) {
+        const int c = static_cast<int8_t>((v >> (8 * i)) & 0xFFu);
+        const uint32_t neg = c < 0 ? 1u : 0u;
+        const uint32_t mag = static_cast<uint32_t>(c < 0 ? -c : c);
+        if (mag > 14u) *bad = true;
+        r |= static_cast<uint64_t>((neg << 5) | (((mag | 1u) ^ (neg << 1)) & 0x1Fu)) << (8 * i);
+    }
+    return r;
+}
+
 // Fills the table; every thread of the group calls it (tid in [0, nthreads)).
 // Returns true when this thread saw an entry that the XOR decode cannot represent.
 __device__ inline bool lut_fill(uint32_t lut_addr, const void *cb, int cb_is_f16, int convention,
-                                uint32_t extra, int tid, int nthreads) {
+                                int fmt, int tid, int nthreads) {
     bool bad = false;
     for (int i = tid; i < 512; i += nthreads) {
         const int e = i >> 1;
         const int part = i & 1;
-        const uint64_t v = part == 0 ? load_entry(cb, cb_is_f16, e, &bad)
-                                     : sign_mask(static_cast<uint32_t>(e), convention, extra);
+        const uint64_t v = part == 0 ? format_entry(load_entry(cb, cb_is_f16, e, &bad), fmt, &bad)
+                                     : sign_mask(static_cast<uint32_t>(e), convention, fmt);
         const uint32_t lo = static_cast<uint32_t>(v), hi = static_cast<uint32_t>(v >> 32);
         const uint4 rep = make_uint4(lo, hi, lo, hi);
         const uint32_t base = lut_addr + static_cast<uint32_t>(e) * 256u + static_cast<uint32_t>(part) * 128u;

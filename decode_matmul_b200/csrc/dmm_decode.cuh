@@ -22,7 +22,7 @@ __global__ void __launch_bounds__(kDecodeThreads) decode_kernel(const uint32_t *
         if (threadIdx.x == 0) raise_status(DMM_STATUS_BAD_SMEM);
         return;
     }
-    const bool bad = lut_fill(lut_addr, cb, cb_is_f16, sign_convention, kF16 ? 0x80u : 0x00u, threadIdx.x,
+    const bool bad = lut_fill(lut_addr, cb, cb_is_f16, sign_convention, kF16 ? kFmtOffset : kFmtTwos, threadIdx.x,
                               kDecodeThreads);
     if (bad) raise_status(DMM_STATUS_BAD_CODEBOOK);
     __syncthreads();

@@ -48,8 +48,10 @@ extern "C" {
 #define DMM_LAYOUT_FAST 1 /* uint32 [N/32][K/16][32] layout, used by fast_decode_matmul_cuda */
 
 #define DMM_PATH_AUTO 0
-#define DMM_PATH_GEMV 1    /* CUDA-core/legacy-MMA streaming path, any M */
-#define DMM_PATH_TCGEN05 2 /* tcgen05 + TMEM path, M >= 16 */
+#define DMM_PATH_GEMV 1       /* streaming kernel on warp-level MMAs, any M */
+#define DMM_PATH_TCGEN05 2    /* tcgen05 + TMEM, decoded weights as fp16 operands, any M */
+#define DMM_PATH_TCGEN05_F8 3 /* tcgen05 + TMEM, weights as fp6 and activations as exact fp8 planes;
+                                 the small-batch path, taken per chunk of 8 batch columns */
 
 /* launch flags (bit mask) */
 #define DMM_FLAG_ACCUMULATE 1u /* out += result instead of out = result */
@@ -104,7 +106,7 @@ size_t dmm_workspace_bytes(int64_t M, int64_t N, int64_t K);
  */
 int dmm_status(unsigned *status_out);
 
-/* Which path DMM_PATH_AUTO resolves to for this shape (DMM_PATH_GEMV or DMM_PATH_TCGEN05). */
+/* Which path DMM_PATH_AUTO resolves to for this shape (one of the DMM_PATH_* values above). */
 int dmm_select_path(int64_t M, int64_t N, int64_t K);
 
 /* Number of kernels the library has launched in this process (all devices, all entry points). */

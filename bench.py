@@ -1,0 +1,343 @@
+#!/usr/bin/env python
+"""Benchmark of the decode-matmul hot path on the Llama-2-70B linear stack.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--batch B] [--impl ours|reference]
+
+One step = one pass of a [B, 8192] residual stream through the linear layers of 80
+transformer blocks (qkv 10240x8192, o 8192x8192, gate+up 57344x8192, down 8192x28672; 17.1 GB
+of 2-bit codes), synthetic seeded codes and codebook.  With N > 1 (launched by torchrun, one
+rank per GPU) the stack is tensor-parallel: qkv and gate/up split by output rows, o and down
+split by reduction index with an NCCL all-reduce, so the total work is fixed (strong scaling).
+
+The JSON line reports compressed-weight GB/s: code bytes of the whole stack divided by the
+step time.  `value` is timed with the inputs resident in HBM (CUDA-graph replay of the step),
+`e2e` through the public Python API with the activations coming from pinned host memory and
+the result copied back every step.  The weights are far larger than L2 (17 GB vs 126 MB), so
+no flush is needed between steps.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "compressed_weight_hbm_gbs"
+UNIT = "GB/s"
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--layers", type=int, default=80)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    return ap.parse_args()
+
+
+def workload_config(args, world):
+    return {
+        "workload": "llama2-70b-linear-stack (BASELINE.json configs[4]; layer shapes of configs[3])",
+        "shapes": {"qkv": [10240, 8192], "o": [8192, 8192], "gate_up": [57344, 8192], "down": [8192, 28672]},
+        "layers": args.layers,
+        "batch": args.batch,
+        "parallelism": f"tp{world}" if world > 1 else "single",
+        "l2": "inputs larger than L2 (17.1 GB of codes per step), no flush",
+    }
+
+
+# ------------------------------------------------------------------------------------------
+# clocks
+# ------------------------------------------------------------------------------------------
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index=0):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 6:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[2:6]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------------
+# CPU baseline: the reference's path as BASELINE.md defines it (table-gather decode, then an
+# fp32 torch.matmul), timed on the host cores on a bounded sample: one transformer block.
+# ------------------------------------------------------------------------------------------
+def cpu_reference_sample(batch, reps=1):
+    import numpy as np
+    import torch
+
+    from oracle import dmm_oracle as o
+
+    cb16 = o.synthetic_codebook(42)
+    table = (o.decode_table(o.cb16_to_cb64(cb16)).astype(np.float32) / 4)  # [65536, 8]
+    table_t = torch.from_numpy(table)
+    rng = np.random.default_rng(46)
+    shapes = [(10240, 8192), (8192, 8192), (57344, 8192), (8192, 28672)]
+    total_bytes, t_decode, t_matmul = 0, 0.0, 0.0
+    for _ in range(reps):
+        for n, k in shapes:
+            codes = torch.from_numpy(rng.integers(0, 65536, size=(n, k // 8), dtype=np.int64))
+            x = torch.from_numpy(rng.standard_normal((batch, k)).astype(np.float16))
+            t0 = time.perf_counter()
+            w = table_t[codes].reshape(n, k)  # decode: gather of 8 weights per code
+            t1 = time.perf_counter()
+            y = torch.matmul(x.float(), w.t())
+            t2 = time.perf_counter()
+            t_decode += t1 - t0
+            t_matmul += t2 - t1
+            total_bytes += n * k // 4
+            del w, y, codes
+    seconds = t_decode + t_matmul
+    return {
+        "value": total_bytes / seconds / 1e9,
+        "unit": UNIT,
+        "cores": torch.get_num_threads(),
+        "host_cpus": os.cpu_count(),
+        "kind": "port",
+        "sample": f"{reps} transformer block(s) of the stack (4 matmuls, {total_bytes / 1e6:.0f} MB of codes) at batch "
+                  f"{batch}: decode {t_decode:.2f} s + fp32 matmul {t_matmul:.2f} s",
+        "seconds": seconds,
+    }
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    times = []
+    info = None
+    for i in range(args.warmup + args.steps):
+        info = cpu_reference_sample(args.batch, reps=1)
+        if i >= args.warmup:
+            times.append(info["seconds"])
+        if sum(times) > 150:  # keep the whole run within a few minutes
+            break
+    sample_bytes = 213909504
+    sec = statistics.mean(times)
+    value = sample_bytes / sec / 1e9
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": len(times), "warmup": args.warmup,
+        "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic", "impl": "reference",
+        "config": dict(workload_config(args, 1), step="one transformer block (bounded sample of the stack)"),
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": info["cores"], "kind": "port", "sample": info["sample"]},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------
+# our arm
+# ------------------------------------------------------------------------------------------
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    import decode_matmul_b200 as dmm
+    from decode_matmul_b200.linear import LLAMA2_70B, LinearStack
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    cfg = dict(LLAMA2_70B, layers=args.layers)
+    stack = LinearStack(cfg, dmm.synthetic_codebook(42), dev, world=world, rank=rank, seed=46, scale=2.0 ** -12)
+    B, H = args.batch, cfg["hidden"]
+    gen = torch.Generator().manual_seed(1234)
+    h_host = torch.randn(B, H, generator=gen, dtype=torch.float32).pin_memory()
+    out_host = torch.empty(B, H, dtype=torch.float32).pin_memory()
+    h_in = torch.empty(B, H, dtype=torch.float32, device=dev)
+    h = torch.empty(B, H, dtype=torch.float32, device=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(ms):
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- capture one step (residual stream resident in HBM) ----
+    stream = torch.cuda.Stream(dev)
+    h_in.copy_(h_host)
+    with torch.cuda.stream(stream):
+        for _ in range(2):  # allocates the library workspace and NCCL buffers before capture
+            h.copy_(h_in)
+            stack.step(h)
+        stream.synchronize()
+        launches0 = dmm.launch_count()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            h.copy_(h_in)
+            stack.step(h)
+        launches_per_step = dmm.launch_count() - launches0
+    barrier()
+
+    def timed(fn, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(stream):
+            e0.record(stream)
+            for _ in range(steps):
+                fn()
+            e1.record(stream)
+        barrier()
+        return max_over_ranks(e0.elapsed_time(e1)) / steps
+
+    def step_resident():
+        graph.replay()
+
+    def step_e2e():
+        h_in.copy_(h_host, non_blocking=True)
+        graph.replay()
+        out_host.copy_(h, non_blocking=True)
+        stream.synchronize()  # the caller reads the result every step
+
+    with torch.cuda.stream(stream):
+        for _ in range(args.warmup):
+            step_resident()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ms = timed(step_resident, args.steps)
+    with torch.cuda.stream(stream):
+        for _ in range(args.warmup):
+            step_e2e()
+    ms_e2e = timed(step_e2e, args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+
+    # ---- dominant kernel alone: every matmul of the stack back to back, no glue ----
+    xs = {k: torch.randn(B, lin.in_features, device=dev, dtype=torch.float16) for k, lin in stack.layers[0].items()}
+    outs = {k: torch.empty(B, lin.out_features, device=dev, dtype=torch.float32) for k, lin in stack.layers[0].items()}
+
+    def kernels_only():
+        for blk in stack.layers:
+            for k, lin in blk.items():
+                lin(xs[k], out=outs[k])
+
+    with torch.cuda.stream(stream):
+        kernels_only()
+        kgraph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(kgraph, stream=stream):
+            kernels_only()
+    ms_kernels = timed(kgraph.replay, max(3, args.steps // 4))
+    status = dmm.status()
+
+    if rank == 0:
+        from oracle import dmm_oracle  # noqa: F401  (the checker; used below for the CPU baseline only)
+
+        code_bytes = stack.code_bytes_total
+        value = code_bytes / (ms * 1e-3) / 1e9
+        e2e = code_bytes / (ms_e2e * 1e-3) / 1e9
+        # algorithmic bytes of the matmul launches of this rank: codes + activations + outputs + codebook
+        alg = 0
+        for blk in stack.layers:
+            for lin in blk.values():
+                alg += lin.code_bytes + 2 * B * lin.in_features + 4 * B * lin.out_features + 4096
+        peaks = {}
+        try:
+            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        except (OSError, ValueError):
+            pass
+        peak = float(peaks.get("hbm_gbs", 6650.0))
+        achieved = alg / (ms_kernels * 1e-3) / 1e9
+        cpu = cpu_reference_sample(B, reps=1)
+        cpu.pop("seconds")
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "f16 x 2-bit codes (fp6/fp8 tensor-core operands, fp32 accumulate)", "data": "synthetic",
+            "config": workload_config(args, world),
+            "e2e": {"value": e2e, "unit": UNIT, "ms_per_step": ms_e2e, "h2d_bytes_per_step": B * H * 4,
+                    "d2h_bytes_per_step": B * H * 4},
+            "gpu_launches": int(launches_per_step) * args.steps,
+            "gpu_launches_per_step": int(launches_per_step),
+            "tokens_per_s": B / (ms * 1e-3),
+            "pct_of_8tbs": 100.0 * value / 8000.0 / world,
+            "roofline": {
+                "bound": "hbm", "achieved": achieved, "peak": peak,
+                "peak_source": "MEASURED_PEAKS.json hbm_gbs (of measured)" if peaks else "6650 GB/s (of fallback)",
+                "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                "kernel": "umma_kernel<PolF8,32>" if B <= 8 else "umma_kernel<PolF16,*>",
+                "how": "all matmul launches of the stack back to back in one CUDA graph, CUDA events; per-GPU figure",
+                "ms": ms_kernels,
+            },
+            "cpu_baseline": cpu,
+            "clocks": clocks,
+            "status_word": status,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    args = parse()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -10,8 +10,10 @@
 //                         produced by the table XOR alone, 6 instructions per code), the
 //                         fp16 activations split EXACTLY into four E5M2 planes (the top byte
 //                         of the half, then of the remainder, ...), kind::f8f6f4, K = 32.
-//                         Four MMAs per k-tile are free at this batch size; the decode, the
-//                         actual limiter of a 2-bit-per-weight stream, is at its minimum.
+//                         The four planes are stacked along the MMA n dimension (n = 8*plane
+//                         + batch column, N = 32), so one MMA per k-tile does all of them and
+//                         the epilogue adds the four column groups.  The decode, the actual
+//                         limiter of a 2-bit-per-weight stream, is at its minimum.
 //   PolF16  (batch >= 9)  weights as fp16 integers q (byte -> half by magic number),
 //                         activations as fp16, kind::f16, K = 16.
 //
@@ -22,14 +24,16 @@
 // numbered super-tile-major and split evenly and contiguously over the CTAs (stream-K); the
 // part of a super-tile a CTA owns is a segment.
 //
-// Warp roles (20 warps):
+// Warp roles (22 warps):
 //   0..15  decoders, four groups of four warps.  Group q takes chunks q, q+4, ... (C tiles
 //          each) of a segment.  Warp wq of a group owns TMEM lanes 32wq..32wq+31 = strips
 //          4wq..4wq+3; it streams its own strips through a private TMA ring, decodes, writes
-//          A stage buffers in TMEM and signals the MMA thread.  Groups 0 and 1 also run the
+//          A stage buffers in TMEM and signals its MMA issuer.  Groups 0 and 1 also run the
 //          epilogue of tile 0 and tile 1.
-//   16     MMA issuer (one thread) and TMEM allocation.
-//   17..19 activation loaders.
+//   16..19 MMA issuers (one thread each); issuer s serves the decoder groups q with
+//          q % kNAcc == s and owns accumulator s of both MMA tiles.  Warp 16 also allocates
+//          the tensor memory.
+//   20..21 activation loaders.
 // Every wait is bounded (mbar_wait); nothing spins on another CTA.
 #pragma once
 #include "dmm_common.cuh"
@@ -121,8 +125,9 @@ struct PolF8 {
     static constexpr int kNA = 4;
     static constexpr int kRing = 3;    // chunks in flight per decoder warp
     static constexpr int kACols = 8;   // TMEM columns of one A stage of one MMA tile (32 k x 1 byte)
-    static constexpr int kXS = 24;     // activation stages
-    static constexpr uint32_t x_stage_bytes(int) { return 1024; }  // 4 planes x 2 k-halves x 8 rows x 16 B
+    static constexpr int kXS = 32;     // activation stages
+    static constexpr uint32_t x_stage_bytes(int) { return 1024; }  // 2 k-halves x (4 planes x 8 rows) x 16 B
+    static constexpr int out_cols(int) { return 8; }                // batch columns per launch
 };
 struct PolF16 {
     static constexpr int kIsF8 = 0;
@@ -133,10 +138,11 @@ struct PolF16 {
     static constexpr int kACols = 16;  // 32 k x 2 bytes
     static constexpr int kXS = 12;
     static constexpr uint32_t x_stage_bytes(int nmma) { return static_cast<uint32_t>(nmma) * 64u; }  // 4 k-chunks x rows x 16 B
+    static constexpr int out_cols(int nmma) { return nmma; }
 };
 
-constexpr int kUDecWarps = 16, kUMmaWarp = 16, kULoadWarps = 3;
-constexpr int kUThreads = (kUDecWarps + 1 + kULoadWarps) * 32;
+constexpr int kUDecWarps = 16, kUMmaWarp = 16, kUMmaWarps = 4, kULoadWarps = 2;
+constexpr int kUThreads = (kUDecWarps + kUMmaWarps + kULoadWarps) * 32;
 constexpr uint32_t kUBarBytes = 2048;
 constexpr uint32_t kUTmemCols = 512;
 
@@ -147,12 +153,13 @@ struct UmmaPlan {
     static constexpr uint32_t kACols = 4 * Pol::kNA * 2 * Pol::kACols;
     static_assert(kDCols + kACols <= kUTmemCols, "TMEM plan exceeds 512 columns");
     static constexpr uint32_t kXStage = Pol::x_stage_bytes(NMMA);
-    static constexpr uint32_t kXBytes = Pol::kXS * kXStage + 256;  // + zero block
+    static constexpr uint32_t kXBytes = Pol::kXS * kXStage;
+    static constexpr int kNB = Pol::out_cols(NMMA);               // output columns per launch
     static constexpr uint32_t kPreBytes = kUBarBytes + kXBytes;
     static constexpr uint32_t kSlotBytes = 4 * Pol::kC * 128;    // 4 strips x C k-tiles
     static constexpr uint32_t kRingBytes = kUDecWarps * Pol::kRing * kSlotBytes;
     static constexpr uint32_t kDynBytes = 0x10000u - 0x400u + kLutBytes + kRingBytes;
-    static constexpr int kPartial = 2 * NMMA * 128;              // accumulator values per segment
+    static constexpr int kPartial = 2 * kNB * 128;               // output values per segment
     static_assert(kPreBytes <= 0x10000u - 0x400u, "activation stages do not fit below the table");
     static_assert(kDynBytes <= 232448u, "shared memory plan exceeds the per-CTA limit");
     // barrier indices
@@ -184,14 +191,13 @@ struct UmmaParams {
 template <class Pol, int NMMA>
 __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p) {
     using Plan = UmmaPlan<Pol, NMMA>;
-    constexpr int C = Pol::kC, NA = Pol::kNA, RING = Pol::kRing, XS = Pol::kXS, NACC = Plan::kNAcc;
+    constexpr int C = Pol::kC, NA = Pol::kNA, RING = Pol::kRing, XS = Pol::kXS, NACC = Plan::kNAcc, NB = Plan::kNB;
 
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     const uint32_t base = smem_u32(smem_raw);
     const uint32_t lut_addr = (base + Plan::kPreBytes + 0xFFFFu) & ~0xFFFFu;
     const uint32_t ring_addr = lut_addr + kLutBytes;
     const uint32_t x_addr = base + kUBarBytes;
-    const uint32_t zero_addr = x_addr + XS * Plan::kXStage;
     volatile int *flags = reinterpret_cast<volatile int *>(smem_raw + Plan::kBarCount * 8);  // [0]=failed [1]=last
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem_raw + Plan::kBarCount * 8 + 16);
     auto bar = [&](int i) -> uint32_t { return base + 8u * static_cast<uint32_t>(i); };
@@ -231,7 +237,7 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p) 
             mbar_init(bar(Plan::kBarXFull + i), 1);
             mbar_init(bar(Plan::kBarXFree + i), 1);
         }
-        mbar_init(bar(Plan::kBarDReady), 1);
+        mbar_init(bar(Plan::kBarDReady), NACC);
         mbar_init(bar(Plan::kBarDFree), 8);
         flags[0] = 0;
         flags[1] = 0;
@@ -369,9 +375,9 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p) 
                 const int nacc = nchunks < NACC ? nchunks : NACC;
                 mbar_wait(bar(Plan::kBarDReady), static_cast<uint32_t>(segidx & 1), flags);
                 tc_fence_after();
-                float v[NMMA];
+                float v[NB];
 #pragma unroll
-                for (int b = 0; b < NMMA; ++b) v[b] = 0.f;
+                for (int b = 0; b < NB; ++b) v[b] = 0.f;
 #pragma unroll
                 for (int a = 0; a < NACC; ++a) {
                     if (a < nacc) {
@@ -380,8 +386,9 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p) 
                             uint32_t r[16];
                             tmem_ld16(tlane + static_cast<uint32_t>((q * NACC + a) * NMMA + b0), r);
                             tmem_wait_ld();
+                            // PolF8: column 8*plane + b; PolF16: column b
 #pragma unroll
-                            for (int e = 0; e < 16; ++e) v[b0 + e] += __uint_as_float(r[e]);
+                            for (int e = 0; e < 16; ++e) v[(b0 + e) % NB] += __uint_as_float(r[e]);
                         }
                     }
                 }
@@ -398,7 +405,7 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p) 
                 if (full) {
                     if (n < p.N) {
 #pragma unroll
-                        for (int b = 0; b < NMMA; ++b)
+                        for (int b = 0; b < NB; ++b)
                             if (b < p.M) {
                                 float *o = p.out + b * p.N + n;
                                 const float r = p.scale * v[b];
@@ -406,9 +413,9 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p) 
                             }
                     }
                 } else {
-                    float *mine = p.partials + (cta * 2 + my_slot) * Plan::kPartial + q * NMMA * 128 + trow;
+                    float *mine = p.partials + (cta * 2 + my_slot) * Plan::kPartial + q * NB * 128 + trow;
 #pragma unroll
-                    for (int b = 0; b < NMMA; ++b)
+                    for (int b = 0; b < NB; ++b)
                         if (b < p.M) mine[b * 128] = v[b];
                     __threadfence();
                     named_barrier(2, 256);
@@ -425,12 +432,12 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p) 
                         __threadfence();
                         if (n < p.N) {
 #pragma unroll
-                            for (int b = 0; b < NMMA; ++b)
+                            for (int b = 0; b < NB; ++b)
                                 if (b < p.M) {
                                     float tot = 0.f;
                                     for (long long c = c_lo; c <= c_hi; ++c) {
                                         const int slot_c = part_begin(T, G, c) > ss_a ? 0 : 1;
-                                        tot += __ldcg(p.partials + (c * 2 + slot_c) * Plan::kPartial + (q * NMMA + b) * 128 +
+                                        tot += __ldcg(p.partials + (c * 2 + slot_c) * Plan::kPartial + (q * NB + b) * 128 +
                                                       trow);
                                     }
                                     float *o = p.out + b * p.N + n;
@@ -443,58 +450,50 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p) 
                 }
             }
         }
-    } else if (warp == kUMmaWarp) {
-        // =============================== MMA issuer ===============================
-        if (lane == 0) {
-            uint32_t sA[4] = {0, 0, 0, 0};
-            uint32_t xi = 0;
+    } else if (warp < kUMmaWarp + kUMmaWarps) {
+        // =============================== MMA issuers ===============================
+        const int me = warp - kUMmaWarp;  // accumulator index this issuer owns
+        if (lane == 0 && me < NACC) {
+            uint32_t cnt[4] = {0, 0, 0, 0};  // A stages consumed per decoder group (only own groups advance)
             int segidx = 0;
             const uint32_t idesc = Pol::kIsF8
                                        ? ((1u << 4) | (3u << 7) | (1u << 10) | ((NMMA >> 3) << 17) | ((128u >> 4) << 24))
                                        : ((1u << 4) | ((NMMA >> 3) << 17) | ((128u >> 4) << 24));
+            // descriptor of activation stage 0; later stages and k-halves only move the address field
+            const uint64_t xdesc0 = Pol::kIsF8 ? smem_desc(x_addr, 512, 128) : smem_desc(x_addr, NMMA * 16, 128);
+            uint32_t xi = 0;  // CTA-wide tile counter (every issuer counts all tiles)
             for (int ss = ss_first; ss <= ss_last; ++ss, ++segidx) {
                 const int len = seg_len(ss);
                 if (segidx > 0) {
                     mbar_wait(bar(Plan::kBarDFree), static_cast<uint32_t>((segidx - 1) & 1), flags);
                     tc_fence_after();
                 }
-                uint32_t used = 0;  // bit a: accumulator a already holds data of this segment
-                for (int j = 0; j < len; ++j) {
-                    const int q = (j / C) & 3, acc = q % NACC;
-                    const uint32_t cnt = q == 0 ? sA[0] : q == 1 ? sA[1] : q == 2 ? sA[2] : sA[3];
-                    const int buf = static_cast<int>(cnt % NA);
-                    const int xs = static_cast<int>(xi % XS);
-                    mbar_wait(bar(Plan::kBarAFull + q * NA + buf), (cnt / NA) & 1, flags);
+                uint32_t on = 0;  // accumulator already holds data of this segment
+                for (int j = 0; j < len; ++j, ++xi) {
+                    const int q = (j / C) & 3;
+                    if (q % NACC != me) continue;
+                    const uint32_t c = q < 2 ? cnt[q] : cnt[q];
+                    const int buf = static_cast<int>(c % NA);
+                    const uint32_t xs = xi % XS;
+                    mbar_wait(bar(Plan::kBarAFull + q * NA + buf), (c / NA) & 1, flags);
                     mbar_wait(bar(Plan::kBarXFull + xs), (xi / XS) & 1, flags);
                     tc_fence_after();
-                    const uint32_t xst = x_addr + xs * Plan::kXStage;
+                    const uint64_t xd = xdesc0 + ((xs * Plan::kXStage) >> 4);
                     const uint32_t a_col = tmem + Plan::kDCols + static_cast<uint32_t>(q * NA + buf) * 2 * Pol::kACols;
-                    uint32_t on = (used >> acc) & 1u;
 #pragma unroll
                     for (int t = 0; t < 2; ++t) {
-                        const uint32_t d_col = tmem + static_cast<uint32_t>((t * NACC + acc) * NMMA);
-                        uint32_t acc_on = on;
+                        const uint32_t d_col = tmem + static_cast<uint32_t>((t * NACC + me) * NMMA);
                         if constexpr (Pol::kIsF8) {
-#pragma unroll
-                            for (int pl = 0; pl < 4; ++pl) {
-                                const uint32_t pb = xst + pl * 256;
-                                mma_ts_f8(d_col, a_col + t * Pol::kACols, smem_desc(pb, 128, zero_addr - pb), idesc, acc_on);
-                                acc_on = 1;
-                            }
+                            mma_ts_f8(d_col, a_col + t * Pol::kACols, xd, idesc, on);
                         } else {
-#pragma unroll
-                            for (int kh = 0; kh < 2; ++kh) {
-                                mma_ts_f16(d_col, a_col + t * Pol::kACols + 8 * kh,
-                                           smem_desc(xst + kh * 2 * (NMMA * 16), NMMA * 16, 128), idesc, acc_on);
-                                acc_on = 1;
-                            }
+                            mma_ts_f16(d_col, a_col + t * Pol::kACols, xd, idesc, on);
+                            mma_ts_f16(d_col, a_col + t * Pol::kACols + 8, xd + ((2 * NMMA * 16) >> 4), idesc, 1u);
                         }
                     }
-                    used |= 1u << acc;
+                    on = 1;
                     tc_commit(bar(Plan::kBarAFree + q * NA + buf));
                     tc_commit(bar(Plan::kBarXFree + xs));
-                    if (q == 0) ++sA[0]; else if (q == 1) ++sA[1]; else if (q == 2) ++sA[2]; else ++sA[3];
-                    ++xi;
+                    ++cnt[q];
                 }
                 tc_commit(bar(Plan::kBarDReady));
             }
@@ -502,7 +501,7 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p) 
     } else {
         // =========================== activation loaders ===========================
         grid_dep_wait();
-        const int wl = warp - kUMmaWarp - 1;
+        const int wl = warp - kUMmaWarp - kUMmaWarps;
         const __half *x = reinterpret_cast<const __half *>(p.x);
         const int M = static_cast<int>(p.M);
         // CTA-wide tile stream in processing order: segment by segment, k-tile by k-tile
@@ -562,11 +561,12 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p) 
                     if (u < u_n && have[u]) {
                         if (active) {
                             uint32_t h[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
-                            const uint32_t dst = x_addr + stage[u] * Plan::kXStage + (kc >> 1) * 128 + row * 16 + (kc & 1) * 8;
+                            // stage layout [k-half][8*plane + row][16 B]
+                            const uint32_t dst = x_addr + stage[u] * Plan::kXStage + (kc >> 1) * 512 + row * 16 + (kc & 1) * 8;
 #pragma unroll
                             for (int pl = 0; pl < 4; ++pl) {
                                 // plane pl = top byte of each half (an E5M2 number), then subtract it
-                                sts64(dst + pl * 256, prmt(h[0], h[1], 0x7531u), prmt(h[2], h[3], 0x7531u));
+                                sts64(dst + pl * 128, prmt(h[0], h[1], 0x7531u), prmt(h[2], h[3], 0x7531u));
 #pragma unroll
                                 for (int e = 0; e < 4; ++e) {
                                     const uint32_t top = h[e] & 0xFF00FF00u;
@@ -657,7 +657,7 @@ inline int launch_umma_one(const UmmaParams &p_in, int num_sms, bool pdl, cudaSt
 
 // f8 != 0: PolF8 (needs M <= 8); else PolF16 with M <= 64.
 inline int launch_umma(bool f8, const UmmaParams &p, int num_sms, bool pdl, cudaStream_t stream) {
-    if (f8) return launch_umma_one<PolF8, 16>(p, num_sms, pdl, stream);
+    if (f8) return launch_umma_one<PolF8, 32>(p, num_sms, pdl, stream);
     if (p.M <= 16) return launch_umma_one<PolF16, 16>(p, num_sms, pdl, stream);
     if (p.M <= 32) return launch_umma_one<PolF16, 32>(p, num_sms, pdl, stream);
     return launch_umma_one<PolF16, 64>(p, num_sms, pdl, stream);
@@ -665,8 +665,8 @@ inline int launch_umma(bool f8, const UmmaParams &p, int num_sms, bool pdl, cuda
 
 // Workspace floats per CTA slot for a batch of M columns on this path.
 inline int umma_partial_values(long long M, bool f8) {
-    const int nmma = f8 ? 16 : (M <= 16 ? 16 : (M <= 32 ? 32 : 64));
-    return 2 * nmma * 128;
+    const int nb = f8 ? 8 : (M <= 16 ? 16 : (M <= 32 ? 32 : 64));
+    return 2 * nb * 128;
 }
 
 }  // namespace dmm

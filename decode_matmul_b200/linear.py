@@ -1,0 +1,120 @@
+"""Quantised linear layers over the decode-matmul operator, and the Llama-style stack of them.
+
+``DecodeLinear`` holds one weight matrix as tile-packed codes plus codebook and scale.
+``LinearStack`` chains the four projections of a transformer block (qkv, o, gate+up, down)
+for a number of layers and shards them over the ranks of a tensor-parallel group:
+qkv and gate/up are column-parallel (split N: a contiguous byte range of the tiled codes),
+o and down are row-parallel (split K: tile-packed per shard) followed by an all-reduce.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib, ops
+from .layout import shard_cols, shard_rows, transpose_tile
+
+
+class DecodeLinear:
+    """y = scale * x @ W^T with W stored as 2-bit-per-weight codes (fp16 family).
+
+    ``codes`` is the LOGICAL int16 [N, K/8] matrix; it is tile-packed here, once."""
+
+    def __init__(self, codes: torch.Tensor, codebook_fp16: torch.Tensor, scale: float = 1.0, *, tiled: bool = False):
+        self.codes = codes.contiguous() if tiled else transpose_tile(codes)
+        self.codebook = codebook_fp16.contiguous()
+        self.scale = float(scale)
+        self.out_features = self.codes.shape[0]
+        self.in_features = self.codes.shape[1] * 8
+
+    @property
+    def code_bytes(self) -> int:
+        return self.codes.numel() * 2
+
+    def to(self, device):
+        self.codes = self.codes.to(device)
+        self.codebook = self.codebook.to(device)
+        return self
+
+    def __call__(self, x: torch.Tensor, out: torch.Tensor | None = None, accumulate: bool = False,
+                 path: int = _lib.PATH_AUTO, pdl: bool = True) -> torch.Tensor:
+        return ops.decode_matmul_fp16(x, self.codes, self.codebook, self.scale, out, path=path,
+                                      accumulate=accumulate, pdl=pdl)
+
+
+def llama_shapes(hidden: int, kv_heads: int, head_dim: int, ffn: int) -> dict:
+    """(N, K) of the four fused projections of one block."""
+    return {
+        "qkv": (hidden + 2 * kv_heads * head_dim, hidden),
+        "o": (hidden, hidden),
+        "gate_up": (2 * ffn, hidden),
+        "down": (hidden, ffn),
+    }
+
+
+LLAMA2_70B = dict(hidden=8192, kv_heads=8, head_dim=128, ffn=28672, layers=80)
+LLAMA2_7B = dict(hidden=4096, kv_heads=32, head_dim=128, ffn=11008, layers=32)
+
+
+class LinearStack:
+    """The linear layers of ``layers`` transformer blocks with synthetic (seeded) codes.
+
+    Data flow of one step for a [B, hidden] fp32 residual stream h:
+        a = qkv(fp16(h));  h += o(fp16(a[:, :hidden]))          (attention itself is not part of
+        g = gate_up(fp16(h));  h += down(fp16(silu(g0) * g1))    the operator: q stands in for it)
+    Row-parallel outputs are summed over the tensor-parallel group before the residual add.
+    The weights are generated directly in sharded form: rank r of w draws its own codes, so
+    that no rank ever materialises a full matrix."""
+
+    def __init__(self, cfg: dict, codebook_fp16: torch.Tensor, device, world: int = 1, rank: int = 0,
+                 seed: int = 46, scale: float = 2.0 ** -7, group=None):
+        self.cfg, self.world, self.rank, self.group = cfg, world, rank, group
+        self.device = torch.device(device)
+        self.hidden, self.ffn = cfg["hidden"], cfg["ffn"]
+        shapes = llama_shapes(cfg["hidden"], cfg["kv_heads"], cfg["head_dim"], cfg["ffn"])
+        for name, (n, k) in shapes.items():
+            div = n if name in ("qkv", "gate_up") else k
+            if div % (32 * world) or (name in ("qkv", "gate_up") and n % (16 * world)):
+                raise RuntimeError(f"{name} does not shard over {world} ranks")
+        self.shapes = shapes
+        cb = codebook_fp16.to(self.device)
+        gen = torch.Generator(device=self.device).manual_seed(seed * 1000 + rank)
+        self.layers = []
+        self.code_bytes_local = 0
+        for _ in range(cfg["layers"]):
+            block = {}
+            for name, (n, k) in shapes.items():
+                if name in ("qkv", "gate_up"):
+                    n_loc, k_loc = n // world, k
+                else:
+                    n_loc, k_loc = n, k // world
+                # uniform int16 codes; any bit pattern is a valid tile-packed matrix, so the
+                # shard is drawn directly in tiled form
+                codes = torch.randint(-32768, 32768, (n_loc, k_loc // 8), dtype=torch.int16, device=self.device,
+                                      generator=gen)
+                block[name] = DecodeLinear(codes, cb, scale, tiled=True)
+                self.code_bytes_local += block[name].code_bytes
+            self.layers.append(block)
+        self.code_bytes_total = sum(n * k // 4 for n, k in shapes.values()) * cfg["layers"]
+        self.launches_per_step = 4 * cfg["layers"]
+
+    def step(self, h: torch.Tensor, path: int = _lib.PATH_AUTO) -> torch.Tensor:
+        """One pass of the stack over the fp32 residual stream ``h`` [B, hidden] (updated in place)."""
+        hid_loc = self.hidden // self.world
+        ffn_loc = self.ffn // self.world
+        for blk in self.layers:
+            a = blk["qkv"](h.to(torch.float16), path=path)
+            # row-parallel o: this rank's slice of the attention output stands in for attention
+            a16 = a[:, :hid_loc].to(torch.float16).contiguous()
+            self._row_parallel(blk["o"], a16, h, path)
+            g = blk["gate_up"](h.to(torch.float16), path=path)
+            act = (torch.nn.functional.silu(g[:, :ffn_loc]) * g[:, ffn_loc:]).to(torch.float16)
+            self._row_parallel(blk["down"], act, h, path)
+        return h
+
+    def _row_parallel(self, lin: DecodeLinear, x16: torch.Tensor, h: torch.Tensor, path: int) -> None:
+        if self.world == 1:
+            lin(x16, out=h, accumulate=True, path=path)
+            return
+        part = lin(x16, path=path)
+        torch.distributed.all_reduce(part, group=self.group)
+        h.add_(part)

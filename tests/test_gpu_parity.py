@@ -127,18 +127,57 @@ def _check_f16(y, want):
     assert rel <= REL_L2, f"rel L2 {rel}"
 
 
+PATHS = {"legacy-mma": dmm.PATH_GEMV, "tcgen05-f16": dmm.PATH_TCGEN05, "tcgen05-f8": dmm.PATH_TCGEN05_F8,
+         "auto": dmm.PATH_AUTO}
+
+
+@pytest.mark.parametrize("path", sorted(PATHS))
 @pytest.mark.parametrize("M,N,K", F16_SHAPES)
-def test_fp16_family(M, N, K):
+def test_fp16_family(M, N, K, path):
     rng = np.random.default_rng(M * 7 + N * 13 + K)
     cb16 = o.synthetic_codebook(42)
     x = rng.standard_normal((M, K)).astype(np.float16)
     codes = _codes(rng, N, K)
     want = o.decode_matmul_f16(x, codes, cb16, 1.0)
     tiled, cb = _dev(o.tile_pack(codes)), _dev(cb16)
-    for _ in range(2):
-        y = dmm.decode_matmul_fp16(_dev(x), tiled, cb, 1.0, path=dmm.PATH_GEMV)
+    for _ in range(2):  # the second call checks that the workspace counters were reset
+        y = dmm.decode_matmul_fp16(_dev(x), tiled, cb, 1.0, path=PATHS[path])
         assert y.dtype == torch.float32
         _check_f16(y.cpu().numpy(), want)
+
+
+@pytest.mark.parametrize("path", ["tcgen05-f16", "tcgen05-f8"])
+def test_fp16_family_large_batch_and_accumulate(path):
+    rng = np.random.default_rng(5)
+    M, N, K = 70, 272, 1056  # more than one batch chunk, a partial super-tile, K not a multiple of 128
+    cb16 = o.synthetic_codebook(3)
+    x = rng.standard_normal((M, K)).astype(np.float16)
+    codes = _codes(rng, N, K)
+    base = rng.standard_normal((M, N)).astype(np.float32)
+    out = _dev(base)
+    y = dmm.decode_matmul_fp16(_dev(x), _dev(o.tile_pack(codes)), _dev(cb16), 0.125, out, path=PATHS[path],
+                               accumulate=True, sign_convention=dmm.SIGN_FAST)
+    assert y.data_ptr() == out.data_ptr()
+    _check_f16(y.cpu().numpy(), base + o.decode_matmul_f16(x, codes, cb16, 0.125, o.SIGN_FAST))
+
+
+def test_fp8_plane_split_is_exact_for_awkward_activations():
+    """Subnormal, tiny, huge and all-mantissa-bits halves: the four E5M2 planes must add up exactly."""
+    rng = np.random.default_rng(9)
+    M, N, K = 4, 256, 512
+    cb16 = o.synthetic_codebook(42)
+    bits = rng.integers(0, 0x7C00, size=(M, K)).astype(np.uint16)  # every finite positive half pattern
+    bits[1] |= 0x8000
+    bits[2, ::2] = rng.integers(0, 0x0400, size=K // 2).astype(np.uint16)  # subnormals
+    x = (bits.view(np.float16).astype(np.float32) * np.float32(2.0 ** -10)).astype(np.float16)
+    codes = _codes(rng, N, K)
+    want = o.decode_matmul_f16(x, codes, cb16, 1.0)
+    y = dmm.decode_matmul_fp16(_dev(x), _dev(o.tile_pack(codes)), _dev(cb16), 1.0, path=dmm.PATH_TCGEN05_F8)
+    y2 = dmm.decode_matmul_fp16(_dev(x), _dev(o.tile_pack(codes)), _dev(cb16), 1.0, path=dmm.PATH_TCGEN05)
+    got, got2 = y.cpu().numpy(), y2.cpu().numpy()
+    scale = np.abs(want).max()
+    assert np.abs(got - want).max() <= 2e-5 * scale + 1e-6   # fp8-operand MMA: fewer accumulator bits
+    assert np.abs(got2 - want).max() <= 2e-6 * scale + 1e-6
 
 
 def test_fp16_family_scale_e8p_and_linearity(e8p):
@@ -148,11 +187,22 @@ def test_fp16_family_scale_e8p_and_linearity(e8p):
     x = rng.standard_normal((M, K)).astype(np.float16)
     codes = _codes(rng, N, K)
     tiled, cb = _dev(o.tile_pack(codes)), _dev(cb16)
-    y = dmm.decode_matmul_fp16(_dev(x), tiled, cb, 0.5).cpu().numpy()
-    _check_f16(y, o.decode_matmul_f16(x, codes, cb16, 0.5))
-    # linearity in the scale and in x (exact powers of two)
-    y2 = dmm.decode_matmul_fp16(_dev((x * np.float16(2)).astype(np.float16)), tiled, cb, 0.25).cpu().numpy()
-    assert np.array_equal(y, y2)
+    want = o.decode_matmul_f16(x, codes, cb16, 0.5)
+    x2 = _dev((x * np.float16(2)).astype(np.float16))
+    for name, path in PATHS.items():
+        y = dmm.decode_matmul_fp16(_dev(x), tiled, cb, 0.5, path=path).cpu().numpy()
+        _check_f16(y, want)
+        again = dmm.decode_matmul_fp16(_dev(x), tiled, cb, 0.5, path=path).cpu().numpy()
+        assert np.array_equal(y, again), f"{name}: two identical calls differ"
+        # linearity in the scale (exact: a power of two) and in x (exact where the operands are fp16;
+        # the fp8-operand MMA keeps fewer accumulator bits, so there only to rounding)
+        half = dmm.decode_matmul_fp16(_dev(x), tiled, cb, 0.25, path=path).cpu().numpy()
+        assert np.array_equal(y, 2 * half)
+        y2 = dmm.decode_matmul_fp16(x2, tiled, cb, 0.25, path=path).cpu().numpy()
+        if name in ("legacy-mma", "tcgen05-f16"):
+            assert np.array_equal(y, y2)
+        else:
+            assert np.abs(y - y2).max() <= 1e-3
 
 
 def test_bad_codebook_raises_status():

@@ -16,7 +16,7 @@ FLAG_ACCUMULATE, FLAG_PDL = 1, 2
 STATUS_WAIT_TIMEOUT, STATUS_BAD_CODEBOOK, STATUS_BAD_SMEM = 1, 2, 4
 
 EXPORTS = (
-    "dmm_i8", "dmm_f16", "dmm_decode", "dmm_workspace_bytes", "dmm_status", "dmm_select_path",
+    "dmm_i8", "dmm_f16", "dmm_f16_noalloc", "dmm_decode", "dmm_workspace_bytes", "dmm_status", "dmm_select_path",
     "dmm_launch_count", "dmm_error_string", "dmm_version",
 )
 
@@ -39,6 +39,8 @@ def lib() -> ctypes.CDLL:
     L.dmm_i8.restype = ci
     L.dmm_f16.argtypes = [vp, vp, vp, ctypes.c_float, vp, i64, i64, i64, ci, ci, ci, cu, vp, sz, vp]
     L.dmm_f16.restype = ci
+    L.dmm_f16_noalloc.argtypes = [vp, vp, vp, ctypes.c_float, vp, i64, i64, i64, ci, cu, vp]
+    L.dmm_f16_noalloc.restype = ci
     L.dmm_decode.argtypes = [vp, vp, ci, vp, i64, i64, ci, ci, vp]
     L.dmm_decode.restype = ci
     L.dmm_workspace_bytes.argtypes = [i64, i64, i64]

@@ -164,6 +164,38 @@ static int run_umma(bool f8, const void *x, const void *codes, const void *cb16,
     return 0;
 }
 
+// ---------------------------------------------------------------------------------------
+// Fixed scratch for dmm_f16_noalloc: ticket counters, then stream-K partials for up to
+// kNoAllocMaxCtas CTAs of the fp8-operand tcgen05 kernel (2 slots x 2048 floats each).
+// A file-scope device array: every GPU that loads the library carries it until exit.
+// ---------------------------------------------------------------------------------------
+constexpr int kNoAllocMaxCtas = 160;
+constexpr long long kNoAllocMaxM = 8;
+constexpr long long kNoAllocMaxN = 262144;  // 1024 super-tiles -> 4 KiB of tickets
+constexpr size_t kNoAllocTicketBytes = 4096;
+constexpr size_t kNoAllocBytes = kNoAllocTicketBytes + static_cast<size_t>(kNoAllocMaxCtas) * 2 * 2048 * sizeof(float);
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocBytes];
+static void *g_noalloc_ptr[kMaxDevices];  // device address of the array, per device, set on first use
+
+// Device address of g_noalloc_scratch on the current device.  In host code the array's name
+// is only a handle; the address a kernel can use comes from cudaGetSymbolAddress, asked once
+// per device with that device current.
+static int noalloc_scratch(void **out) {
+    int dev = 0;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess) return err;
+    if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+    std::lock_guard<std::mutex> lock(g_mutex);
+    if (g_noalloc_ptr[dev] == nullptr) {
+        void *ptr = nullptr;
+        err = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+        if (err != cudaSuccess) return err;
+        g_noalloc_ptr[dev] = ptr;
+    }
+    *out = g_noalloc_ptr[dev];
+    return 0;
+}
+
 }  // namespace dmm
 
 using namespace dmm;
@@ -194,6 +226,42 @@ int dmm_f16(const void *x, const int16_t *codes, const void *cb16, float scale, 
     // the kernels accumulate quarter units: fold the 1/4 into the scale
     return run_stream(1, x, codes, cb16, 1, 0.25f * scale, out, M, N, K, sign_convention, flags, workspace,
                       workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+int dmm_f16_noalloc(const void *x, const int16_t *codes, const void *cb16, float scale, float *out, int64_t M,
+                    int64_t N, int64_t K, int sign_convention, unsigned flags, void *stream) {
+    int rc = check_common(x, codes, cb16, out, M, N, K, sign_convention, DMM_LAYOUT_TILE);
+    if (rc) return rc;
+    if (M > kNoAllocMaxM || N > kNoAllocMaxN) return DMM_ERR_LIMIT;
+    DeviceState *d = nullptr;
+    rc = current_device_state(&d);
+    if (rc) return rc;
+    void *ws = nullptr;
+    rc = noalloc_scratch(&ws);
+    if (rc) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // The array keeps whatever the previous call left.  Partials are always written before
+    // they are read; the ticket counters must start at zero, so clear them (a call that was
+    // cut short by a device-side timeout could have left some behind).
+    cudaError_t err = cudaMemsetAsync(ws, 0, kNoAllocTicketBytes, st);
+    if (err != cudaSuccess) return err;
+    UmmaParams p = {};
+    p.x = x;
+    p.codes = codes;
+    p.cb = cb16;
+    p.out = out;
+    p.tickets = reinterpret_cast<unsigned *>(ws);
+    p.partials = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(ws) + kNoAllocTicketBytes);
+    p.M = M;
+    p.N = N;
+    p.K = K;
+    p.scale = 2.0f * scale;
+    p.accumulate = (flags & DMM_FLAG_ACCUMULATE) ? 1 : 0;
+    p.sign_convention = sign_convention;
+    const int ctas = d->num_sms < kNoAllocMaxCtas ? d->num_sms : kNoAllocMaxCtas;
+    rc = launch_umma(true, p, ctas, (flags & DMM_FLAG_PDL) != 0, st);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return rc;
 }
 
 int dmm_decode(const int16_t *codes, const void *cb, int cb_is_f16, void *W_out, int64_t N, int64_t K,
@@ -253,6 +321,7 @@ const char *dmm_error_string(int code) {
         case DMM_ERR_ARG: return "unknown enum value";
         case DMM_ERR_WORKSPACE: return "workspace too small (see dmm_workspace_bytes)";
         case DMM_ERR_UNSUPPORTED: return "shape or layout not implemented by the chosen path";
+        case DMM_ERR_LIMIT: return "size beyond the fixed scratch of dmm_f16_noalloc (M <= 8, N <= 262144)";
         default: break;
     }
     if (code > 0) return cudaGetErrorString(static_cast<cudaError_t>(code));

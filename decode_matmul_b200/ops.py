@@ -91,6 +91,33 @@ def decode_matmul_fp16(x, weights_compressed, codebook_fp16, scale=1.0, output=N
     return output
 
 
+def decode_matmul_fp16_noalloc(x, weights_compressed, codebook_fp16, scale, output, *,
+                               sign_convention=_lib.SIGN_SLOW, accumulate=False, pdl=False):
+    """``decode_matmul_fp16`` for programs that cannot let the library allocate device memory
+    (a server whose pool allocator already owns all of HBM, a latency-critical loop that must
+    not take the allocator lock or the device synchronisation that cudaMalloc implies).  The caller supplies ``output``; the kernel's
+    scratch is a fixed array inside the library, so nothing is allocated here or below.
+    Batch at most 8, N at most 262144.  Calls on one device share that array: do not let two
+    of them overlap on the GPU.  The first call on a device looks up the array's address and should come before any
+    stream capture."""
+    _check_input(x, "x", torch.float16)
+    _check_input(weights_compressed, "weights_compressed", torch.int16)
+    _check_input(codebook_fp16, "codebook_fp16", torch.float16)
+    _check_input(output, "output", torch.float32)
+    _req(x.dim() == 2 and weights_compressed.dim() == 2, "x and weights_compressed must be 2-D")
+    _req(tuple(codebook_fp16.shape) == (256, 8), "codebook_fp16 must have shape [256, 8]")
+    _req(x.size(-1) == weights_compressed.size(-1) << 3, "x.size(-1) must equal 8 * weights_compressed.size(-1)")
+    M, K = x.shape
+    N = weights_compressed.size(0)
+    _req(tuple(output.shape) == (M, N), "output must have shape [M, N]")
+    flags = (_lib.FLAG_ACCUMULATE if accumulate else 0) | (_lib.FLAG_PDL if pdl else 0)
+    with torch.cuda.device(x.device):
+        rc = _lib.lib().dmm_f16_noalloc(_ptr(x), _ptr(weights_compressed), _ptr(codebook_fp16), float(scale),
+                                        _ptr(output), M, N, K, sign_convention, flags, _stream_ptr(x.device))
+    _lib.check(rc, "decode_matmul_fp16_noalloc")
+    return output
+
+
 def decode_weights(weights_compressed, codebook, *, sign_convention=_lib.SIGN_SLOW, layout=_lib.LAYOUT_TILE):
     """Decoded weights in logical order: int8 [N, K] (= 4 * weight) for an int64 codebook,
     fp16 [N, K] for an fp16 codebook."""

@@ -40,6 +40,7 @@ extern "C" {
 #define DMM_ERR_ARG (-4)         /* unknown enum value */
 #define DMM_ERR_WORKSPACE (-5)   /* caller-supplied workspace too small */
 #define DMM_ERR_UNSUPPORTED (-6) /* shape outside what the chosen path implements */
+#define DMM_ERR_LIMIT (-7)       /* size beyond the fixed scratch of dmm_f16_noalloc */
 
 #define DMM_SIGN_SLOW 0
 #define DMM_SIGN_FAST 1
@@ -87,6 +88,30 @@ int dmm_i8(const int8_t *x, const int16_t *codes, const int64_t *cb64, int32_t *
 int dmm_f16(const void *x, const int16_t *codes, const void *cb16, float scale, float *out,
             int64_t M, int64_t N, int64_t K, int sign_convention, int layout, int path,
             unsigned flags, void *workspace, size_t workspace_bytes, void *stream);
+
+/*
+ * dmm_f16 for callers that must not allocate.  (No counterpart in the reference.)
+ *
+ * Some host programs cannot let a library call cudaMalloc on their behalf: a serving
+ * process that has handed all of HBM to its own pool allocator (a later cudaMalloc simply
+ * fails there), or a latency-critical loop that may not take the driver's allocator lock
+ * or the implicit device synchronisation that comes with cudaMalloc and cudaFree.
+ * dmm_f16 needs scratch memory for its stream-K
+ * partial sums and, without a caller-supplied workspace, allocates it lazily.  This entry
+ * point is the small-batch tcgen05 kernel (DMM_PATH_TCGEN05_F8) running on a scratch array
+ * that is compiled into the library as a file-scope __device__ array instead: it calls no
+ * cudaMalloc, no cudaFree and no allocating library routine, ever.
+ *
+ * Limits: M <= 8 and N <= 262144 (DMM_ERR_LIMIT beyond), tile layout only.  The array is
+ * about 2.6 MB and every GPU that loads the library holds it until the process exits.
+ * The first call on each device looks up the array's device address
+ * (cudaGetSymbolAddress); make that first call outside any stream capture.  All calls on
+ * a device share the one array: two calls that can overlap on the GPU (different streams)
+ * race on it and must be serialised by the caller.  Results equal dmm_f16 with
+ * DMM_PATH_TCGEN05_F8.
+ */
+int dmm_f16_noalloc(const void *x, const int16_t *codes, const void *cb16, float scale, float *out,
+                    int64_t M, int64_t N, int64_t K, int sign_convention, unsigned flags, void *stream);
 
 /*
  * Decode only.  W_out[N,K] in logical (row-major) order: int8 (= 4 * weight) when

@@ -4,7 +4,7 @@ The product is the CUDA library ``libdmm.so`` behind the C ABI of ``include/dmm.
 package is its PyTorch-facing host side.  Drop-in modules named like the reference's
 extensions live at the repository root (``decode_matmul_cuda``, ``fast_decode_matmul_cuda``).
 """
-from ._lib import (FLAG_ACCUMULATE, FLAG_PDL, LAYOUT_FAST, LAYOUT_TILE, PATH_AUTO, PATH_GEMV, PATH_TCGEN05, PATH_TCGEN05_F8,
+from ._lib import (FLAG_ACCUMULATE, FLAG_ATOMIC, FLAG_PDL, LAYOUT_FAST, LAYOUT_TILE, PATH_AUTO, PATH_GEMV, PATH_TCGEN05, PATH_TCGEN05_F8,
                    SIGN_FAST, SIGN_SLOW)
 from .codebook import (build_codebook_abs, codebook_from_fp16, codebook_to_fp16, pack_codebook,
                        synthetic_codebook)
@@ -16,5 +16,5 @@ __all__ = [
     "transpose_tile", "untranspose_tile", "shard_rows", "shard_cols",
     "build_codebook_abs", "pack_codebook", "codebook_to_fp16", "codebook_from_fp16", "synthetic_codebook",
     "SIGN_SLOW", "SIGN_FAST", "LAYOUT_TILE", "LAYOUT_FAST", "PATH_AUTO", "PATH_GEMV", "PATH_TCGEN05", "PATH_TCGEN05_F8",
-    "FLAG_ACCUMULATE", "FLAG_PDL",
+    "FLAG_ACCUMULATE", "FLAG_PDL", "FLAG_ATOMIC",
 ]

@@ -12,7 +12,7 @@ _LIB = None
 SIGN_SLOW, SIGN_FAST = 0, 1
 LAYOUT_TILE, LAYOUT_FAST = 0, 1
 PATH_AUTO, PATH_GEMV, PATH_TCGEN05, PATH_TCGEN05_F8 = 0, 1, 2, 3
-FLAG_ACCUMULATE, FLAG_PDL = 1, 2
+FLAG_ACCUMULATE, FLAG_PDL, FLAG_ATOMIC = 1, 2, 4
 STATUS_WAIT_TIMEOUT, STATUS_BAD_CODEBOOK, STATUS_BAD_SMEM = 1, 2, 4
 
 EXPORTS = (

@@ -131,6 +131,10 @@ static int run_stream(int family, const void *x, const void *codes, const void *
     return 0;
 }
 
+#ifdef DMM_TRACE
+static long long *g_trace = nullptr;  // device buffer for clock stamps (debug builds only)
+#endif
+
 // tcgen05 path: one launch per chunk of 64 batch columns (8 for the fp6/fp8 operand policy).
 static int run_umma(bool f8, const void *x, const void *codes, const void *cb16, float scale, float *out, long long M,
                     long long N, long long K, int sign_convention, unsigned flags, void *workspace,
@@ -156,7 +160,11 @@ static int run_umma(bool f8, const void *x, const void *codes, const void *cb16,
         // accumulators hold sum(x * q / 8) (fp6 weights) or sum(x * q) (fp16 weights); weight = q / 4
         p.scale = f8 ? 2.0f * scale : 0.25f * scale;
         p.accumulate = (flags & DMM_FLAG_ACCUMULATE) ? 1 : 0;
+        p.atomic_reduce = (flags & DMM_FLAG_ATOMIC) ? 1 : 0;
         p.sign_convention = sign_convention;
+#ifdef DMM_TRACE
+        p.trace = g_trace;
+#endif
         rc = launch_umma(f8, p, d->num_sms, (flags & DMM_FLAG_PDL) != 0, stream);
         g_launches.fetch_add(1, std::memory_order_relaxed);
         if (rc) return rc;
@@ -329,5 +337,9 @@ const char *dmm_error_string(int code) {
 }
 
 const char *dmm_version(void) { return "0.1"; }
+
+#ifdef DMM_TRACE
+void dmm_debug_set_trace(long long *device_buffer) { g_trace = device_buffer; }
+#endif
 
 }  // extern "C"

@@ -67,7 +67,12 @@ __device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, volatil
     if (mbar_try_wait(bar, parity)) return;
     if (*failed) return;
     const long long t0 = clock64();
-    while (!mbar_try_wait(bar, parity)) {
+    for (;;) {
+        // try_wait suspends the thread for a hardware-defined while: poll a few times between
+        // looks at the clock so that a waiting warp costs almost no issue slots
+#pragma unroll 1
+        for (int i = 0; i < 16; ++i)
+            if (mbar_try_wait(bar, parity)) return;
         if (clock64() - t0 > kWaitLimitCycles || *failed) {
             if (!*failed) {
                 *failed = 1;
@@ -75,6 +80,15 @@ __device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, volatil
             }
             return;
         }
+    }
+}
+
+// A plain bounded wait that ignores the CTA's failed flag: used on the way out of a kernel whose
+// earlier wait gave up, to let copies that are still in flight land.
+__device__ __forceinline__ void mbar_wait_limit(uint32_t bar, uint32_t parity, long long cycles) {
+    const long long t0 = clock64();
+    while (!mbar_try_wait(bar, parity)) {
+        if (clock64() - t0 > cycles) return;
     }
 }
 
@@ -86,6 +100,17 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t
         "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint "
         "[%0], [%1], %2, [%3], %4;" ::"r"(dst),
         "l"(src), "r"(bytes), "r"(bar), "l"(policy)
+        : "memory");
+}
+
+// 2-D tiled TMA load (tensor map in kernel parameter space), completion counted on an mbarrier.
+// x is in elements of the map's data type and x * element size must be a multiple of 16 bytes.
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const void *tmap, int x, int y, uint32_t bar,
+                                            uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint "
+        "[%0], [%1, {%2, %3}], [%4], %5;" ::"r"(dst),
+        "l"(tmap), "r"(x), "r"(y), "r"(bar), "l"(policy)
         : "memory");
 }
 
@@ -199,6 +224,16 @@ __host__ __device__ inline uint64_t sign_mask(uint32_t h, int convention, int fm
     return m;
 }
 
+// kFmtFp6 masks carry two bits per weight, so they are stored as ONE 32-bit word per high
+// byte: weights 0..3 at bits 8j+1 (sign ^ shift) and 8j+5 (sign), weights 4..7 one bit
+// higher.  (word & 0x22222222) and ((word >> 1) & 0x22222222) are the two byte-mask words.
+// A 4-byte look-up is one shared-memory wavefront per warp instead of two.
+__host__ __device__ inline uint32_t sign_mask_fp6_packed(uint32_t h, int convention) {
+    const uint64_t m = sign_mask(h, convention, kFmtFp6);
+    const uint32_t lo = static_cast<uint32_t>(m), hi = static_cast<uint32_t>(m >> 32);
+    return (lo & 0x22222222u) | ((hi & 0x22222222u) << 1);
+}
+
 // Codebook entry e as packed int8 x 8 (= 4 * value), from either table format.  Sets *bad
 // when the entry cannot be decoded by XOR (byte not congruent to 2 mod 4, fp16 value not k/4).
 __device__ inline uint64_t load_entry(const void *cb, int cb_is_f16, int e, bool *bad) {
@@ -238,19 +273,28 @@ __device__ inline uint64_t format_entry(uint64_t v, int fmt, bool *bad) {
 
 // Fills the table; every thread of the group calls it (tid in [0, nthreads)).
 // Returns true when this thread saw an entry that the XOR decode cannot represent.
+// packed_mask: store the kFmtFp6 masks as 32 replicas of the packed 32-bit word.
 __device__ inline bool lut_fill(uint32_t lut_addr, const void *cb, int cb_is_f16, int convention,
-                                int fmt, int tid, int nthreads) {
+                                int fmt, int tid, int nthreads, bool packed_mask = false) {
     bool bad = false;
     for (int i = tid; i < 512; i += nthreads) {
         const int e = i >> 1;
         const int part = i & 1;
-        const uint64_t v = part == 0 ? format_entry(load_entry(cb, cb_is_f16, e, &bad), fmt, &bad)
-                                     : sign_mask(static_cast<uint32_t>(e), convention, fmt);
-        const uint32_t lo = static_cast<uint32_t>(v), hi = static_cast<uint32_t>(v >> 32);
-        const uint4 rep = make_uint4(lo, hi, lo, hi);
+        uint4 rep;
+        if (part == 1 && packed_mask) {
+            const uint32_t w = sign_mask_fp6_packed(static_cast<uint32_t>(e), convention);
+            rep = make_uint4(w, w, w, w);
+        } else {
+            const uint64_t v = part == 0 ? format_entry(load_entry(cb, cb_is_f16, e, &bad), fmt, &bad)
+                                         : sign_mask(static_cast<uint32_t>(e), convention, fmt);
+            const uint32_t lo = static_cast<uint32_t>(v), hi = static_cast<uint32_t>(v >> 32);
+            rep = make_uint4(lo, hi, lo, hi);
+        }
         const uint32_t base = lut_addr + static_cast<uint32_t>(e) * 256u + static_cast<uint32_t>(part) * 128u;
+        // Consecutive threads own consecutive 128-byte half rows (same banks): start each at a
+        // different 16-byte chunk so that a warp-wide store touches every bank equally.
 #pragma unroll
-        for (int r = 0; r < 8; ++r) sts128(base + 16u * r, rep);
+        for (int r = 0; r < 8; ++r) sts128(base + 16u * static_cast<uint32_t>((r + i) & 7), rep);
     }
     return bad;
 }
@@ -259,14 +303,24 @@ __device__ inline bool lut_fill(uint32_t lut_addr, const void *cb, int cb_is_f16
 // the mask half of a row), bytes 2..3 = the table's 64 KiB-aligned shared address.
 struct LutLane {
     uint32_t entry_c;  // lut_addr | (lane%16)*8
-    uint32_t mask_c;   // entry_c | 128
+    uint32_t mask_c;   // lut_addr | 128 | (lane%16)*8, or | lane*4 for packed masks
 };
 
-__device__ __forceinline__ LutLane lut_lane(uint32_t lut_addr, int lane) {
+__device__ __forceinline__ LutLane lut_lane(uint32_t lut_addr, int lane, bool packed_mask = false) {
     LutLane l;
     l.entry_c = lut_addr | (static_cast<uint32_t>(lane & 15) << 3);
-    l.mask_c = l.entry_c | 128u;
+    l.mask_c = packed_mask ? (lut_addr | 128u | (static_cast<uint32_t>(lane) << 2)) : (l.entry_c | 128u);
     return l;
+}
+
+// kFmtFp6 with packed masks: 8-byte entry look-up, 4-byte mask look-up, two XORs.
+template <int which>
+__device__ __forceinline__ uint2 decode8_fp6(uint32_t word, const LutLane &l) {
+    constexpr uint32_t sel_idx = which == 0 ? 0x7604u : 0x7624u;
+    constexpr uint32_t sel_hi = which == 0 ? 0x7614u : 0x7634u;
+    const uint2 e = lds64(prmt(word, l.entry_c, sel_idx));
+    const uint32_t m = lds32(prmt(word, l.mask_c, sel_hi));
+    return make_uint2(e.x ^ (m & 0x22222222u), e.y ^ ((m >> 1) & 0x22222222u));
 }
 
 // Decodes the code in half `which` (0 = low 16 bits, 1 = high) of `word`: 8 packed bytes.
@@ -293,6 +347,19 @@ __device__ __forceinline__ void bytes_to_half2(uint2 d, uint32_t (&r)[4]) {
         h = __hsub2(h, bias);
         r[i] = *reinterpret_cast<uint32_t *>(&h);
     }
+}
+
+// ---------------------------------------------------------------------------------------
+// Balanced partition of T work items over G CTAs in 32-bit arithmetic (T < 2^31):
+// with a = T / G and b = T % G (computed on the host), the first b CTAs own a + 1 items.
+// ---------------------------------------------------------------------------------------
+struct Part32 {
+    int a, b;
+};
+__host__ __device__ inline int part32_begin(Part32 pt, int c) { return pt.a * c + (c < pt.b ? c : pt.b); }
+__host__ __device__ inline int part32_owner(Part32 pt, int i) {
+    const int big = pt.b * (pt.a + 1);
+    return i < big ? i / (pt.a + 1) : pt.b + (i - big) / pt.a;
 }
 
 // ---------------------------------------------------------------------------------------

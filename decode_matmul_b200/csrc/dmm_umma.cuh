@@ -36,6 +36,8 @@
 //   20..21 activation loaders.
 // Every wait is bounded (mbar_wait); nothing spins on another CTA.
 #pragma once
+#include <cuda.h>
+
 #include "dmm_common.cuh"
 #include "dmm_launch.h"
 
@@ -118,57 +120,62 @@ __device__ __forceinline__ void sts64(uint32_t addr, uint32_t a, uint32_t b) {
 }
 
 // ----------------------------------- policies -----------------------------------------
+// kG  k-tiles per "group": the unit of decoder -> issuer hand-over (one barrier round trip,
+//     one tcgen05.commit).  Every tcgen05 instruction costs its issuing thread ~45-55 cycles
+//     whatever its size, so hand-overs and commits are amortised over as many MMAs as fit.
+// kNA group buffers per decoder group in TMEM;  kC k-tiles per TMA chunk (multiple of kG).
 struct PolF8 {
     static constexpr int kIsF8 = 1;
     static constexpr int kFmt = kFmtFp6;
-    static constexpr int kC = 4;       // tiles per chunk (= TMEM A stages per group)
-    static constexpr int kNA = 4;
+    static constexpr int kG = 2;
+    static constexpr int kNA = 3;
+    static constexpr int kC = 4;
     static constexpr int kRing = 3;    // chunks in flight per decoder warp
-    static constexpr int kACols = 8;   // TMEM columns of one A stage of one MMA tile (32 k x 1 byte)
-    static constexpr int kXS = 32;     // activation stages
-    static constexpr uint32_t x_stage_bytes(int) { return 1024; }  // 2 k-halves x (4 planes x 8 rows) x 16 B
+    static constexpr int kACols = 8;   // TMEM columns of one k-tile of one MMA tile (32 k x 1 byte)
+    static constexpr uint32_t x_tile_bytes(int) { return 1024; }  // 2 k-halves x (4 planes x 8 rows) x 16 B
     static constexpr int out_cols(int) { return 8; }                // batch columns per launch
 };
 struct PolF16 {
     static constexpr int kIsF8 = 0;
     static constexpr int kFmt = kFmtOffset;
-    static constexpr int kC = 2;
+    static constexpr int kG = 1;
     static constexpr int kNA = 2;
+    static constexpr int kC = 2;
     static constexpr int kRing = 6;
     static constexpr int kACols = 16;  // 32 k x 2 bytes
-    static constexpr int kXS = 12;
-    static constexpr uint32_t x_stage_bytes(int nmma) { return static_cast<uint32_t>(nmma) * 64u; }  // 4 k-chunks x rows x 16 B
+    static constexpr uint32_t x_tile_bytes(int nmma) { return static_cast<uint32_t>(nmma) * 64u; }  // 4 k-chunks x rows x 16 B
     static constexpr int out_cols(int nmma) { return nmma; }
 };
 
-constexpr int kUDecWarps = 16, kUMmaWarp = 16, kUMmaWarps = 4, kULoadWarps = 2;
+constexpr int kUDecWarps = 16, kUMmaWarp = 16, kUMmaWarps = 2, kULoadWarps = 2;
 constexpr int kUThreads = (kUDecWarps + kUMmaWarps + kULoadWarps) * 32;
 constexpr uint32_t kUBarBytes = 2048;
 constexpr uint32_t kUTmemCols = 512;
 
 template <class Pol, int NMMA>
 struct UmmaPlan {
-    static constexpr int kNAcc = NMMA <= 32 ? 4 : 2;             // accumulators per MMA tile
-    static constexpr uint32_t kDCols = 2 * kNAcc * NMMA;         // TMEM: accumulators first
-    static constexpr uint32_t kACols = 4 * Pol::kNA * 2 * Pol::kACols;
+    static constexpr int kNAcc = 2;                               // accumulators per MMA tile = issuers
+    static constexpr uint32_t kDCols = 2 * kNAcc * NMMA;          // TMEM: accumulators first
+    static constexpr uint32_t kBufCols = 2 * Pol::kG * Pol::kACols;  // one group buffer: [tile][k-tile][cols]
+    static constexpr uint32_t kACols = 4 * Pol::kNA * kBufCols;
     static_assert(kDCols + kACols <= kUTmemCols, "TMEM plan exceeds 512 columns");
-    static constexpr uint32_t kXStage = Pol::x_stage_bytes(NMMA);
-    static constexpr uint32_t kXBytes = Pol::kXS * kXStage;
+    static constexpr int kSlots = 4 * Pol::kNA;                   // group buffers = activation stages
+    static constexpr uint32_t kXStage = Pol::kG * Pol::x_tile_bytes(NMMA);
+    static constexpr uint32_t kXBytes = kSlots * kXStage;
     static constexpr int kNB = Pol::out_cols(NMMA);               // output columns per launch
     static constexpr uint32_t kPreBytes = kUBarBytes + kXBytes;
-    static constexpr uint32_t kSlotBytes = 4 * Pol::kC * 128;    // 4 strips x C k-tiles
+    static constexpr uint32_t kSlotBytes = 4 * Pol::kC * 128;     // ring slot: 4 strips x C k-tiles
     static constexpr uint32_t kRingBytes = kUDecWarps * Pol::kRing * kSlotBytes;
     static constexpr uint32_t kDynBytes = 0x10000u - 0x400u + kLutBytes + kRingBytes;
-    static constexpr int kPartial = 2 * kNB * 128;               // output values per segment
+    static constexpr int kPartial = 2 * kNB * 128;                // output values per segment
     static_assert(kPreBytes <= 0x10000u - 0x400u, "activation stages do not fit below the table");
     static_assert(kDynBytes <= 232448u, "shared memory plan exceeds the per-CTA limit");
+    static_assert(Pol::kC % Pol::kG == 0, "a chunk must hold whole groups");
     // barrier indices
-    static constexpr int kBarCode = 0;                                   // [16][kRing]
-    static constexpr int kBarAFull = kBarCode + kUDecWarps * Pol::kRing;  // [4][kNA]
-    static constexpr int kBarAFree = kBarAFull + 4 * Pol::kNA;
-    static constexpr int kBarXFull = kBarAFree + 4 * Pol::kNA;           // [kXS]
-    static constexpr int kBarXFree = kBarXFull + Pol::kXS;
-    static constexpr int kBarDReady = kBarXFree + Pol::kXS;
+    static constexpr int kBarCode = 0;                                   // [16][kRing]  TMA completion
+    static constexpr int kBarFull = kBarCode + kUDecWarps * Pol::kRing;  // [kSlots] 4 decoder warps + 1 loader
+    static constexpr int kBarFree = kBarFull + kSlots;                   // [kSlots] tcgen05.commit
+    static constexpr int kBarDReady = kBarFree + kSlots;
     static constexpr int kBarDFree = kBarDReady + 1;
     static constexpr int kBarCount = kBarDFree + 1;
     static_assert(kBarCount * 8 + 64 <= kUBarBytes, "barrier block too small");
@@ -184,14 +191,30 @@ struct UmmaParams {
     long long M, N, K;
     float scale;         // includes the unit of the accumulators (1/4 for q, 2 for q/8)
     int accumulate;
+    int atomic_reduce;   // partial super-tiles are added to `out` with red.global.add (out must hold the
+                         // value to add to): no workspace round trip, summation order not fixed
     int sign_convention;
+    Part32 part;         // tiles per CTA: part.a = T / grid, part.b = T % grid
     unsigned dyn_smem_bytes;
+    long long *trace;    // debugging aid (builds with -DDMM_TRACE only): clock stamps of CTA 0
 };
 
+#ifdef DMM_TRACE
+#define DMM_STAMP(role, idx, what)                                                              \
+    do {                                                                                        \
+        if (p.trace != nullptr && blockIdx.x == 0 && (idx) < 64) p.trace[((role)*64 + (idx)) * 4 + (what)] = clock64(); \
+    } while (0)
+#else
+#define DMM_STAMP(role, idx, what) do { } while (0)
+#endif
+
+// `codes_map` is a 2-D tensor map of the tiled code matrix: inner dimension = one strip
+// (K/32 k-tiles x 32 uint32), outer dimension = strips; box = kC k-tiles x 4 strips.
 template <class Pol, int NMMA>
-__global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p) {
+__global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
+                                                            const __grid_constant__ CUtensorMap codes_map) {
     using Plan = UmmaPlan<Pol, NMMA>;
-    constexpr int C = Pol::kC, NA = Pol::kNA, RING = Pol::kRing, XS = Pol::kXS, NACC = Plan::kNAcc, NB = Plan::kNB;
+    constexpr int C = Pol::kC, G = Pol::kG, NA = Pol::kNA, RING = Pol::kRing, NACC = Plan::kNAcc, NB = Plan::kNB;
 
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     const uint32_t base = smem_u32(smem_raw);
@@ -203,6 +226,7 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p) 
     auto bar = [&](int i) -> uint32_t { return base + 8u * static_cast<uint32_t>(i); };
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    if (tid == 0) DMM_STAMP(0, 0, 0);
 
     if (ring_addr + Plan::kRingBytes > base + p.dyn_smem_bytes) {  // uniform over the grid
         if (tid == 0) raise_status(DMM_STATUS_BAD_SMEM);
@@ -210,57 +234,58 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p) 
     }
 
     const int KT = static_cast<int>(p.K / 32);
-    const int NS = static_cast<int>(p.N / 16);
-    const int SST = (NS + 15) / 16;  // super-tiles
-    const long long T = static_cast<long long>(SST) * KT;
-    const long long G = gridDim.x, cta = blockIdx.x;
-    const long long i0 = part_begin(T, G, cta), i1 = part_begin(T, G, cta + 1);
-    const int ss_first = static_cast<int>(i0 / KT), ss_last = static_cast<int>((i1 - 1) / KT);
-    auto seg_begin = [&](int ss) -> long long {
-        const long long a = static_cast<long long>(ss) * KT;
-        return i0 > a ? i0 : a;
+    const int cta = blockIdx.x;
+    const int i0 = part32_begin(p.part, cta), i1 = part32_begin(p.part, cta + 1);  // this CTA's tiles
+    const int ss_first = i0 / KT, ss_last = (i1 - 1) / KT;
+    // segment ss of this CTA: first k-tile and number of k-tiles
+    auto seg_kt0 = [&](int ss) -> int {
+        const int a = ss * KT;
+        return i0 > a ? i0 - a : 0;
     };
     auto seg_len = [&](int ss) -> int {
-        const long long a = static_cast<long long>(ss) * KT;
-        const long long lo = i0 > a ? i0 : a, hi = i1 < a + KT ? i1 : a + KT;
-        return static_cast<int>(hi - lo);
+        const int a = ss * KT;
+        const int lo = i0 > a ? i0 : a, hi = i1 < a + KT ? i1 : a + KT;
+        return hi - lo;
     };
+    auto seg_chunks = [&](int ss) -> int { return (seg_len(ss) + C - 1) / C; };
+    // Chunks are numbered through all segments of the CTA (cbase = chunks of earlier segments);
+    // chunk number mod 4 is the decoder group and mod 2 the issuer, so consecutive chunks always
+    // go to different groups, also across a segment boundary.
 
+    if (tid == 0) DMM_STAMP(0, 2, 0);
     // ---- set-up: barriers, TMEM, zeroed activation stages ----
-    if (tid == 0) {
-        for (int i = 0; i < kUDecWarps * RING; ++i) mbar_init(bar(Plan::kBarCode + i), 1);
-        for (int i = 0; i < 4 * NA; ++i) {
-            mbar_init(bar(Plan::kBarAFull + i), 4);
-            mbar_init(bar(Plan::kBarAFree + i), 1);
+    if (tid < Plan::kBarCount) {
+        uint32_t count = 1;                                                  // TMA, tcgen05.commit
+        if (tid >= Plan::kBarFull && tid < Plan::kBarFree) count = 5;         // 4 decoder warps + loader
+        if (tid == Plan::kBarDReady) count = NACC;
+        if (tid == Plan::kBarDFree) count = 8;
+        mbar_init(bar(tid), count);
+        if (tid == 0) {
+            flags[0] = 0;
+            flags[1] = 0;
         }
-        for (int i = 0; i < XS; ++i) {
-            mbar_init(bar(Plan::kBarXFull + i), 1);
-            mbar_init(bar(Plan::kBarXFree + i), 1);
-        }
-        mbar_init(bar(Plan::kBarDReady), NACC);
-        mbar_init(bar(Plan::kBarDFree), 8);
-        flags[0] = 0;
-        flags[1] = 0;
         fence_mbar_init();
     }
+    if (tid == 0) DMM_STAMP(0, 2, 1);
     if (warp == kUMmaWarp) tmem_alloc(smem_u32(const_cast<uint32_t *>(tmem_slot)), kUTmemCols);
     for (uint32_t o = tid * 16u; o < Plan::kXBytes; o += kUThreads * 16u) sts128(x_addr + o, make_uint4(0, 0, 0, 0));
     fence_async_smem();
     tc_fence_before();
+    if (tid == 0) DMM_STAMP(0, 2, 2);
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
     grid_dep_launch();
+    if (tid == 0) DMM_STAMP(0, 0, 1);
 
     if (warp < kUDecWarps) {
         // =============================== decoders ===============================
         const int q = warp >> 2, wq = warp & 3;
         const uint32_t wring = ring_addr + static_cast<uint32_t>(warp) * (RING * Plan::kSlotBytes);
         const uint64_t policy = policy_evict_first();
-        const uint8_t *codes = reinterpret_cast<const uint8_t *>(p.codes);
 
         struct Cur {
-            int ss, c;
+            int ss, c, cbase;  // segment, chunk inside it, chunks of earlier segments
             bool ok;
         };
         auto settle = [&](Cur &cu) {  // first chunk of group q at or after (ss, c)
@@ -268,73 +293,86 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p) 
                 if (cu.ss == ss_last) {
                     cu.ok = false;
                 } else {
+                    cu.cbase += seg_chunks(cu.ss);
                     ++cu.ss;
-                    cu.c = q;
+                    cu.c = (q - cu.cbase) & 3;
                 }
             }
         };
+        // one tiled TMA load per chunk: kC k-tiles x this warp's 4 strips (always the full box:
+        // k-tiles past the segment are simply not used, strips past N read as zero)
         auto issue = [&](const Cur &cu, int idx) {
-            const int len = seg_len(cu.ss);
-            const int n = len - cu.c * C < C ? len - cu.c * C : C;
-            const int kt = static_cast<int>(seg_begin(cu.ss) - static_cast<long long>(cu.ss) * KT) + cu.c * C;
-            const int strip = cu.ss * 16 + wq * 4 + lane;  // lanes 0..3
-            const int nvalid = NS - (cu.ss * 16 + wq * 4);  // strips of this warp that exist
-            const int ns = nvalid < 0 ? 0 : (nvalid > 4 ? 4 : nvalid);
-            const uint32_t b = bar(Plan::kBarCode + warp * RING + idx % RING);
-            if (lane == 0) mbar_arrive_expect_tx(b, static_cast<uint32_t>(n * 128 * ns));
-            __syncwarp();
-            if (lane < ns)
-                bulk_g2s(wring + (idx % RING) * Plan::kSlotBytes + lane * (C * 128),
-                         codes + (static_cast<long long>(strip) * KT + kt) * 128, static_cast<uint32_t>(n * 128), b,
-                         policy);
+            if (lane == 0) {
+                const int kt = seg_kt0(cu.ss) + cu.c * C;
+                const uint32_t b = bar(Plan::kBarCode + warp * RING + idx % RING);
+                mbar_arrive_expect_tx(b, Plan::kSlotBytes);
+                tma_load_2d(wring + (idx % RING) * Plan::kSlotBytes, &codes_map, kt * 32, cu.ss * 16 + wq * 4, b, policy);
+            }
         };
 
-        Cur icur{ss_first, q, true}, ccur;
+        if (tid == 0) DMM_STAMP(0, 3, 0);
+        Cur icur{ss_first, q, 0, true}, ccur;
         settle(icur);
         ccur = icur;
         int iidx = 0, cidx = 0;
+        if (tid == 0) DMM_STAMP(0, 3, 1);
         while (iidx < RING && icur.ok) {  // weights do not depend on the previous kernel
             issue(icur, iidx);
+            if (tid == 0) DMM_STAMP(0, 3, 2);
             icur.c += 4;
             settle(icur);
             ++iidx;
         }
+        if (tid == 0) DMM_STAMP(0, 1, 0);
 
-        const bool bad = lut_fill(lut_addr, p.cb, 1, p.sign_convention, Pol::kFmt, tid, kUDecWarps * 32);
+        const bool bad = lut_fill(lut_addr, p.cb, 1, p.sign_convention, Pol::kFmt, tid, kUDecWarps * 32, Pol::kIsF8 != 0);
         if (bad) raise_status(DMM_STATUS_BAD_CODEBOOK);
+        if (tid == 0) DMM_STAMP(0, 1, 1);
         named_barrier(1, kUDecWarps * 32);
-        const LutLane ll = lut_lane(lut_addr, lane);
+        const LutLane ll = lut_lane(lut_addr, lane, Pol::kIsF8 != 0);
         grid_dep_wait();
+        if (tid == 0) DMM_STAMP(0, 0, 2);
 
         const uint32_t tlane = tmem + (static_cast<uint32_t>(wq * 32) << 16);
-        const uint32_t a_base = Plan::kDCols + static_cast<uint32_t>(q * NA) * 2 * Pol::kACols;
-        uint32_t sA = 0;
-        int segidx = 0;
-        for (int ss = ss_first; ss <= ss_last; ++ss, ++segidx) {
+        uint32_t sA = 0;  // groups this decoder group has produced
+        int segidx = 0, ebase = 0;
+        for (int ss = ss_first; ss <= ss_last; ebase += seg_chunks(ss), ++ss, ++segidx) {
             while (ccur.ok && ccur.ss == ss) {
                 const int len = seg_len(ss);
-                const int n = len - ccur.c * C < C ? len - ccur.c * C : C;
+                const int n = len - ccur.c * C < C ? len - ccur.c * C : C;  // k-tiles in this chunk
                 const int slot = cidx % RING;
                 mbar_wait(bar(Plan::kBarCode + warp * RING + slot), static_cast<uint32_t>((cidx / RING) & 1), flags);
                 const uint32_t src = wring + slot * Plan::kSlotBytes + (lane >> 3) * (C * 128) + (lane & 7) * 16;
-                for (int i = 0; i < n; ++i) {
+#pragma unroll 1
+                for (int g0 = 0; g0 < n; g0 += G) {
                     const int buf = static_cast<int>(sA % NA);
-                    if (sA >= NA) mbar_wait(bar(Plan::kBarAFree + q * NA + buf), ((sA / NA) - 1) & 1, flags);
+                    const int sl = q * NA + buf;
+                    if (tid == 0) DMM_STAMP(1, sA, 0);
+                    if (sA >= NA) mbar_wait(bar(Plan::kBarFree + sl), ((sA / NA) - 1) & 1, flags);
                     tc_fence_after();
-                    const uint4 cw = lds128(src + i * 128);
-                    const uint32_t w[4] = {cw.x, cw.y, cw.z, cw.w};
-                    const uint32_t acol = tlane + a_base + static_cast<uint32_t>(buf) * 2 * Pol::kACols;
+                    if (tid == 0) DMM_STAMP(1, sA, 1);
+                    const uint32_t acol = tlane + Plan::kDCols + static_cast<uint32_t>(sl) * Plan::kBufCols;
                     if constexpr (Pol::kIsF8) {
-                        uint32_t r0[8], r1[8];
+                        // group buffer columns: [tile][k-tile][8]; two k-tiles -> one x16 store per tile
+                        uint32_t r0[8 * G], r1[8 * G];
 #pragma unroll
-                        for (int t = 0; t < 4; ++t) {
-                            const uint2 d0 = decode8<0>(w[t], ll), d1 = decode8<1>(w[t], ll);
-                            r0[2 * t] = d0.x; r0[2 * t + 1] = d0.y;
-                            r1[2 * t] = d1.x; r1[2 * t + 1] = d1.y;
+                        for (int i = 0; i < G; ++i) {
+                            uint4 cw = make_uint4(0, 0, 0, 0);
+                            if (g0 + i < n) cw = lds128(src + (g0 + i) * 128);
+                            const uint32_t w[4] = {cw.x, cw.y, cw.z, cw.w};
+#pragma unroll
+                            for (int t = 0; t < 4; ++t) {
+                                const uint2 d0 = decode8_fp6<0>(w[t], ll), d1 = decode8_fp6<1>(w[t], ll);
+                                r0[8 * i + 2 * t] = d0.x; r0[8 * i + 2 * t + 1] = d0.y;
+                                r1[8 * i + 2 * t] = d1.x; r1[8 * i + 2 * t + 1] = d1.y;
+                            }
                         }
-                        tmem_st8(acol, r0);
-                        tmem_st8(acol + Pol::kACols, r1);
+                        static_assert(G == 2 || !Pol::kIsF8, "fp8 policy stores two k-tiles at once");
+                        tmem_st16(acol, reinterpret_cast<const uint32_t(&)[16]>(r0));
+                        tmem_st16(acol + G * Pol::kACols, reinterpret_cast<const uint32_t(&)[16]>(r1));
                     } else {
+                        const uint4 cw = lds128(src + g0 * 128);
+                        const uint32_t w[4] = {cw.x, cw.y, cw.z, cw.w};
                         uint32_t r0[16], r1[16];
 #pragma unroll
                         for (int t = 0; t < 4; ++t) {
@@ -348,12 +386,14 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p) 
                             }
                         }
                         tmem_st16(acol, r0);
-                        tmem_st16(acol + Pol::kACols, r1);
+                        tmem_st16(acol + G * Pol::kACols, r1);
                     }
+                    if (tid == 0) DMM_STAMP(1, sA, 2);
                     tmem_wait_st();
                     tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(bar(Plan::kBarAFull + q * NA + buf));
+                    if (lane == 0) mbar_arrive(bar(Plan::kBarFull + sl));
+                    if (tid == 0) DMM_STAMP(1, sA, 3);
                     ++sA;
                 }
                 __syncwarp();  // every lane has read the slot: refill it
@@ -372,15 +412,18 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p) 
                 // ---------------- epilogue of MMA tile q of this segment ----------------
                 const int len = seg_len(ss);
                 const int nchunks = (len + C - 1) / C;
-                const int nacc = nchunks < NACC ? nchunks : NACC;
+                // accumulator a was written in this segment iff one of its chunks has parity a
+                const uint32_t used = nchunks >= 2 ? 3u : (1u << (ebase & 1));
+                if (tid == 0) DMM_STAMP(4, segidx, 0);
                 mbar_wait(bar(Plan::kBarDReady), static_cast<uint32_t>(segidx & 1), flags);
                 tc_fence_after();
+                if (tid == 0) DMM_STAMP(4, segidx, 1);
                 float v[NB];
 #pragma unroll
                 for (int b = 0; b < NB; ++b) v[b] = 0.f;
 #pragma unroll
                 for (int a = 0; a < NACC; ++a) {
-                    if (a < nacc) {
+                    if ((used >> a) & 1u) {
 #pragma unroll
                         for (int b0 = 0; b0 < NMMA; b0 += 16) {
                             uint32_t r[16];
@@ -396,13 +439,19 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p) 
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar(Plan::kBarDFree));
 
-                const long long ss_a = static_cast<long long>(ss) * KT;
+                const int ss_a = ss * KT;
                 const bool full = len == KT;
-                const int my_slot = seg_begin(ss) > ss_a ? 0 : 1;
+                const int my_slot = seg_kt0(ss) > 0 ? 0 : 1;
                 const int trow = wq * 32 + lane;  // TMEM lane = row of the MMA tile
                 const long long n = (static_cast<long long>(ss) * 16 + wq * 4 + (lane >> 3)) * 16 + 8 * q + (lane & 7);
                 const int ptid = q * 128 + trow;
-                if (full) {
+                if (p.atomic_reduce) {
+                    if (n < p.N) {
+#pragma unroll
+                        for (int b = 0; b < NB; ++b)
+                            if (b < p.M) atomicAdd(p.out + b * p.N + n, p.scale * v[b]);
+                    }
+                } else if (full) {
                     if (n < p.N) {
 #pragma unroll
                         for (int b = 0; b < NB; ++b)
@@ -413,13 +462,13 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p) 
                             }
                     }
                 } else {
-                    float *mine = p.partials + (cta * 2 + my_slot) * Plan::kPartial + q * NB * 128 + trow;
+                    float *mine = p.partials + static_cast<long long>(cta * 2 + my_slot) * Plan::kPartial + q * NB * 128 + trow;
 #pragma unroll
                     for (int b = 0; b < NB; ++b)
                         if (b < p.M) mine[b * 128] = v[b];
                     __threadfence();
                     named_barrier(2, 256);
-                    const long long c_lo = part_owner(T, G, ss_a), c_hi = part_owner(T, G, ss_a + KT - 1);
+                    const int c_lo = part32_owner(p.part, ss_a), c_hi = part32_owner(p.part, ss_a + KT - 1);
                     if (ptid == 0) {
                         const unsigned expected = static_cast<unsigned>(c_hi - c_lo + 1);
                         const unsigned old = atomicAdd(p.tickets + ss, 1u);
@@ -431,14 +480,26 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p) 
                     if (flags[1] != 0) {
                         __threadfence();
                         if (n < p.N) {
+                            const int ncta = c_hi - c_lo + 1;
 #pragma unroll
                             for (int b = 0; b < NB; ++b)
                                 if (b < p.M) {
+                                    // fixed summation order; eight loads in flight at a time
                                     float tot = 0.f;
-                                    for (long long c = c_lo; c <= c_hi; ++c) {
-                                        const int slot_c = part_begin(T, G, c) > ss_a ? 0 : 1;
-                                        tot += __ldcg(p.partials + (c * 2 + slot_c) * Plan::kPartial + (q * NB + b) * 128 +
-                                                      trow);
+                                    for (int c0 = 0; c0 < ncta; c0 += 8) {
+                                        float part[8];
+#pragma unroll
+                                        for (int e = 0; e < 8; ++e) {
+                                            part[e] = 0.f;
+                                            if (c0 + e < ncta) {
+                                                const int c = c_lo + c0 + e;
+                                                const int slot_c = part32_begin(p.part, c) > ss_a ? 0 : 1;
+                                                part[e] = __ldcg(p.partials + static_cast<long long>(c * 2 + slot_c) * Plan::kPartial +
+                                                                 (q * NB + b) * 128 + trow);
+                                            }
+                                        }
+#pragma unroll
+                                        for (int e = 0; e < 8; ++e) tot += part[e];
                                     }
                                     float *o = p.out + b * p.N + n;
                                     const float r = p.scale * tot;
@@ -448,178 +509,211 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p) 
                     }
                     named_barrier(2, 256);  // flags[1] is reused by the next segment
                 }
+                if (tid == 0) DMM_STAMP(4, segidx, 2);
+            }
+        }
+        if (flags[0]) {
+            // A wait gave up: bulk copies of this warp may still be in flight.  Give each ring
+            // slot a last bounded chance to land before the CTA releases its shared memory.
+            for (int d = 0; d < RING && d < iidx; ++d) {
+                const int idx = iidx - 1 - d;
+                mbar_wait_limit(bar(Plan::kBarCode + warp * RING + idx % RING), static_cast<uint32_t>((idx / RING) & 1),
+                                20ll * 1000 * 1000);
             }
         }
     } else if (warp < kUMmaWarp + kUMmaWarps) {
         // =============================== MMA issuers ===============================
-        const int me = warp - kUMmaWarp;  // accumulator index this issuer owns
-        if (lane == 0 && me < NACC) {
-            uint32_t cnt[4] = {0, 0, 0, 0};  // A stages consumed per decoder group (only own groups advance)
+        // issuer `me` serves decoder groups q with (q & 1) == me and owns accumulator `me`
+        const int me = warp - kUMmaWarp;
+        if (lane == 0) {
+            uint32_t cnt0 = 0, cnt1 = 0;  // groups consumed from decoder groups me and me + 2
             int segidx = 0;
             const uint32_t idesc = Pol::kIsF8
                                        ? ((1u << 4) | (3u << 7) | (1u << 10) | ((NMMA >> 3) << 17) | ((128u >> 4) << 24))
                                        : ((1u << 4) | ((NMMA >> 3) << 17) | ((128u >> 4) << 24));
             // descriptor of activation stage 0; later stages and k-halves only move the address field
             const uint64_t xdesc0 = Pol::kIsF8 ? smem_desc(x_addr, 512, 128) : smem_desc(x_addr, NMMA * 16, 128);
-            uint32_t xi = 0;  // CTA-wide tile counter (every issuer counts all tiles)
-            for (int ss = ss_first; ss <= ss_last; ++ss, ++segidx) {
+            int cbase = 0;
+            for (int ss = ss_first; ss <= ss_last; cbase += seg_chunks(ss), ++ss, ++segidx) {
                 const int len = seg_len(ss);
+                const int nchunks = (len + C - 1) / C;
                 if (segidx > 0) {
                     mbar_wait(bar(Plan::kBarDFree), static_cast<uint32_t>((segidx - 1) & 1), flags);
                     tc_fence_after();
                 }
-                uint32_t on = 0;  // accumulator already holds data of this segment
-                for (int j = 0; j < len; ++j, ++xi) {
-                    const int q = (j / C) & 3;
-                    if (q % NACC != me) continue;
-                    const uint32_t c = q < 2 ? cnt[q] : cnt[q];
-                    const int buf = static_cast<int>(c % NA);
-                    const uint32_t xs = xi % XS;
-                    mbar_wait(bar(Plan::kBarAFull + q * NA + buf), (c / NA) & 1, flags);
-                    mbar_wait(bar(Plan::kBarXFull + xs), (xi / XS) & 1, flags);
-                    tc_fence_after();
-                    const uint64_t xd = xdesc0 + ((xs * Plan::kXStage) >> 4);
-                    const uint32_t a_col = tmem + Plan::kDCols + static_cast<uint32_t>(q * NA + buf) * 2 * Pol::kACols;
+                bool first = true;  // the accumulators hold nothing of this segment yet
+                for (int c = (me - cbase) & 1; c < nchunks; c += 2) {
+                    const int q = (cbase + c) & 3;
+                    const int n = len - c * C < C ? len - c * C : C;
+#pragma unroll 1
+                    for (int g0 = 0; g0 < n; g0 += G) {
+                        const uint32_t cn = q < 2 ? cnt0 : cnt1;
+                        const int sl = q * NA + static_cast<int>(cn % NA);
+                        if (me == 0) DMM_STAMP(2, cn, 0);
+                        mbar_wait(bar(Plan::kBarFull + sl), (cn / NA) & 1, flags);
+                        tc_fence_after();
+                        if (me == 0) DMM_STAMP(2, cn, 1);
+                        const uint64_t xd = xdesc0 + ((static_cast<uint32_t>(sl) * Plan::kXStage) >> 4);
+                        const uint32_t a_col = tmem + Plan::kDCols + static_cast<uint32_t>(sl) * Plan::kBufCols;
 #pragma unroll
-                    for (int t = 0; t < 2; ++t) {
-                        const uint32_t d_col = tmem + static_cast<uint32_t>((t * NACC + me) * NMMA);
-                        if constexpr (Pol::kIsF8) {
-                            mma_ts_f8(d_col, a_col + t * Pol::kACols, xd, idesc, on);
-                        } else {
-                            mma_ts_f16(d_col, a_col + t * Pol::kACols, xd, idesc, on);
-                            mma_ts_f16(d_col, a_col + t * Pol::kACols + 8, xd + ((2 * NMMA * 16) >> 4), idesc, 1u);
+                        for (int t = 0; t < 2; ++t) {
+                            const uint32_t d_col = tmem + static_cast<uint32_t>((t * NACC + me) * NMMA);
+                            uint32_t acc = first ? 0u : 1u;
+                            if constexpr (Pol::kIsF8) {
+#pragma unroll
+                                for (int i = 0; i < G; ++i) {
+                                    if (g0 + i < n) {
+                                        mma_ts_f8(d_col, a_col + (t * G + i) * Pol::kACols, xd + ((i * 1024u) >> 4), idesc, acc);
+                                        acc = 1u;
+                                    }
+                                }
+                            } else {
+                                mma_ts_f16(d_col, a_col + t * G * Pol::kACols, xd, idesc, acc);
+                                mma_ts_f16(d_col, a_col + t * G * Pol::kACols + 8, xd + ((2 * NMMA * 16) >> 4), idesc, 1u);
+                            }
                         }
+                        first = false;
+                        tc_commit(bar(Plan::kBarFree + sl));
+                        if (me == 0) DMM_STAMP(2, cn, 2);
+                        if (q < 2) ++cnt0; else ++cnt1;
                     }
-                    on = 1;
-                    tc_commit(bar(Plan::kBarAFree + q * NA + buf));
-                    tc_commit(bar(Plan::kBarXFree + xs));
-                    ++cnt[q];
                 }
                 tc_commit(bar(Plan::kBarDReady));
             }
         }
     } else {
         // =========================== activation loaders ===========================
+        // loader wl serves the chunks of parity wl (the chunks of issuer wl), one chunk per pass
         grid_dep_wait();
         const int wl = warp - kUMmaWarp - kUMmaWarps;
         const __half *x = reinterpret_cast<const __half *>(p.x);
         const int M = static_cast<int>(p.M);
-        // CTA-wide tile stream in processing order: segment by segment, k-tile by k-tile
-        int cs = ss_first, cj = 0;  // cursor: segment, tile inside it
-        auto kt_of = [&](int ss, int j) -> int {
-            return static_cast<int>(seg_begin(ss) - static_cast<long long>(ss) * KT) + j;
-        };
-        auto skip = [&](int nskip) -> bool {  // advance the cursor; false when the stream ends
-            cj += nskip;
-            while (cj >= seg_len(cs)) {
-                if (cs == ss_last) return false;
-                cj -= seg_len(cs);
-                ++cs;
-            }
-            return true;
-        };
+        const int ppt = M * 4;  // 16-byte pieces per k-tile: (row, 8-k chunk)
+        uint32_t cnt0 = 0, cnt1 = 0;  // groups staged so far for decoder groups wl and wl + 2
+        int cbase = 0;
+
         if constexpr (Pol::kIsF8) {
-            // lanes cover (tile of the batch, piece): piece = (row, 8-k chunk)
-            const int pp = M <= 1 ? 4 : M <= 2 ? 8 : M <= 4 ? 16 : 32;  // lanes per tile
-            const int tb = 32 / pp;                                     // tiles per pass
-            const int u_n = tb >= 4 ? 1 : 4 / tb;                       // passes per batch (loads in flight)
-            const int bt = tb * u_n;                                    // tiles per batch
-            const int piece = lane % pp, tsub = lane / pp;
-            const int row = piece >> 2, kc = piece & 3;
-            const bool active = piece < M * 4;
-            bool more = skip(wl * bt);
-            uint32_t xi = static_cast<uint32_t>(wl * bt);
-            while (more) {
-                uint4 v[4];
-                bool have[4];
-                uint32_t stage[4];
+            // a chunk has at most kC * 8 * 4 = 128 pieces: up to four rounds of 32 lanes; the raw
+            // activations of the NEXT chunk are fetched before the current one is converted
+            constexpr int R = 4;
+            uint4 cur[R], nxt[R];
+            // chunk iterator over (segment, chunk of my parity)
+            int ss = ss_first, c = wl & 1;
+            auto settle = [&]() -> bool {
+                while (c * C >= seg_len(ss)) {
+                    if (ss == ss_last) return false;
+                    cbase += seg_chunks(ss);
+                    ++ss;
+                    c = (wl - cbase) & 1;
+                }
+                return true;
+            };
+            auto fetch = [&](uint4(&v)[R], int fss, int fc) {
+                const int len = seg_len(fss);
+                const int n = len - fc * C < C ? len - fc * C : C;
+                const int kt = seg_kt0(fss) + fc * C;
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    have[u] = false;
-                    if (u < u_n) {
-                        // tile index inside the batch: u * tb + tsub; locate it without moving the cursor
-                        int s2 = cs, j2 = cj + u * tb + tsub;
-                        bool ok = true;
-                        while (j2 >= seg_len(s2)) {
-                            if (s2 == ss_last) { ok = false; break; }
-                            j2 -= seg_len(s2);
-                            ++s2;
-                        }
-                        const uint32_t my_xi = xi + static_cast<uint32_t>(u * tb + tsub);
-                        stage[u] = my_xi % XS;
-                        if (ok) {
-                            if (my_xi >= XS) mbar_wait(bar(Plan::kBarXFree + stage[u]), ((my_xi / XS) - 1) & 1, flags);
-                            have[u] = true;
-                            if (active)
-                                v[u] = __ldg(reinterpret_cast<const uint4 *>(x + static_cast<long long>(row) * p.K +
-                                                                             32 * kt_of(s2, j2) + 8 * kc));
-                        }
+                for (int r = 0; r < R; ++r) {
+                    const int pc = lane + 32 * r;
+                    if (pc < n * ppt) {
+                        const int i = pc / ppt, rem = pc - i * ppt, row = rem >> 2, kc = rem & 3;
+                        v[r] = __ldg(reinterpret_cast<const uint4 *>(x + static_cast<long long>(row) * p.K + 32 * (kt + i) + 8 * kc));
                     }
                 }
+            };
+            bool ok = settle();
+            if (ok) fetch(cur, ss, c);
+            uint32_t pass = 0;
+            while (ok) {
+                const int my_ss = ss, my_c = c, my_cbase = cbase;
+                // look ahead: next chunk of my parity
+                c += 2;
+                const bool more = settle();
+                if (more) fetch(nxt, ss, c);
+                if (wl == 0 && lane == 0) DMM_STAMP(3, pass, 0);
+
+                const int len = seg_len(my_ss);
+                const int n = len - my_c * C < C ? len - my_c * C : C;
+                const int q = (my_cbase + my_c) & 3;
+                const uint32_t cn = q < 2 ? cnt0 : cnt1;
+                const int ngroups = (n + G - 1) / G;
+                for (int gi = 0; gi < ngroups; ++gi) {
+                    const uint32_t cg = cn + gi;
+                    if (cg >= NA) mbar_wait(bar(Plan::kBarFree + q * NA + static_cast<int>(cg % NA)), ((cg / NA) - 1) & 1, flags);
+                }
 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
-                    if (u < u_n && have[u]) {
-                        if (active) {
-                            uint32_t h[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
-                            // stage layout [k-half][8*plane + row][16 B]
-                            const uint32_t dst = x_addr + stage[u] * Plan::kXStage + (kc >> 1) * 512 + row * 16 + (kc & 1) * 8;
+                for (int r = 0; r < R; ++r) {
+                    const int pc = lane + 32 * r;
+                    if (pc < n * ppt) {
+                        const int i = pc / ppt, rem = pc - i * ppt, row = rem >> 2, kc = rem & 3;
+                        const int sl = q * NA + static_cast<int>((cn + i / G) % NA);
+                        uint32_t h[4] = {cur[r].x, cur[r].y, cur[r].z, cur[r].w};
+                        // tile layout [k-half][8*plane + row][16 B]
+                        const uint32_t dst = x_addr + sl * Plan::kXStage + (i % G) * 1024 + (kc >> 1) * 512 + row * 16 + (kc & 1) * 8;
 #pragma unroll
-                            for (int pl = 0; pl < 4; ++pl) {
-                                // plane pl = top byte of each half (an E5M2 number), then subtract it
-                                sts64(dst + pl * 128, prmt(h[0], h[1], 0x7531u), prmt(h[2], h[3], 0x7531u));
+                        for (int pl = 0; pl < 4; ++pl) {
+                            // plane pl = top byte of each half (an E5M2 number), then subtract it
+                            sts64(dst + pl * 128, prmt(h[0], h[1], 0x7531u), prmt(h[2], h[3], 0x7531u));
 #pragma unroll
-                                for (int e = 0; e < 4; ++e) {
-                                    const uint32_t top = h[e] & 0xFF00FF00u;
-                                    __half2 r = __hsub2(*reinterpret_cast<__half2 *>(&h[e]),
-                                                        *reinterpret_cast<const __half2 *>(&top));
-                                    h[e] = *reinterpret_cast<uint32_t *>(&r);
-                                }
+                            for (int e = 0; e < 4; ++e) {
+                                const uint32_t top = h[e] & 0xFF00FF00u;
+                                __half2 rr = __hsub2(*reinterpret_cast<__half2 *>(&h[e]), *reinterpret_cast<const __half2 *>(&top));
+                                h[e] = *reinterpret_cast<uint32_t *>(&rr);
                             }
                         }
-                        fence_async_smem();
                     }
                 }
-                __syncwarp();
-#pragma unroll
-                for (int u = 0; u < 4; ++u)
-                    if (u < u_n && have[u] && piece == 0) mbar_arrive(bar(Plan::kBarXFull + stage[u]));
-                xi += static_cast<uint32_t>(kULoadWarps * bt);
-                more = skip(kULoadWarps * bt);
-            }
-        } else {
-            // warp wl stages tiles wl, wl+3, ...; three tiles in flight per warp
-            bool more = skip(wl);
-            uint32_t xi = static_cast<uint32_t>(wl);
-            uint32_t pend[3] = {0, 0, 0};
-            int npend = 0;
-            auto retire = [&]() {  // oldest pending tile has landed
                 fence_async_smem();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(bar(Plan::kBarXFull + pend[0] % XS));
-                pend[0] = pend[1];
-                pend[1] = pend[2];
+                if (lane < ngroups) mbar_arrive(bar(Plan::kBarFull + q * NA + static_cast<int>((cn + lane) % NA)));
+                if (wl == 0 && lane == 0) DMM_STAMP(3, pass, 1);
+                if (q < 2) cnt0 += ngroups; else cnt1 += ngroups;
+#pragma unroll
+                for (int r = 0; r < R; ++r) cur[r] = nxt[r];
+                ok = more;
+                ++pass;
+            }
+        } else {
+            // fp16 activations: cp.async straight into the stage, two chunks in flight
+            uint32_t pend_q[2] = {0, 0}, pend_cn[2] = {0, 0}, pend_ng[2] = {0, 0};
+            int npend = 0;
+            auto retire = [&]() {  // oldest pending chunk has landed
+                fence_async_smem();
+                __syncwarp();
+                if (lane < static_cast<int>(pend_ng[0]))
+                    mbar_arrive(bar(Plan::kBarFull + static_cast<int>(pend_q[0]) * NA + static_cast<int>((pend_cn[0] + lane) % NA)));
+                pend_q[0] = pend_q[1]; pend_cn[0] = pend_cn[1]; pend_ng[0] = pend_ng[1];
                 --npend;
             };
-            while (more) {
-                const uint32_t st = xi % XS;
-                if (xi >= XS) mbar_wait(bar(Plan::kBarXFree + st), ((xi / XS) - 1) & 1, flags);
-                const int kt = kt_of(cs, cj);
-                const uint32_t dst = x_addr + st * Plan::kXStage;
-                for (int pc = lane; pc < M * 4; pc += 32) {
-                    const int row = pc >> 2, kc = pc & 3;
-                    cp_async16(dst + kc * (NMMA * 16) + row * 16, x + static_cast<long long>(row) * p.K + 32 * kt + 8 * kc);
+            for (int ss = ss_first; ss <= ss_last; cbase += seg_chunks(ss), ++ss) {
+                const int len = seg_len(ss), nchunks = seg_chunks(ss), kt0 = seg_kt0(ss);
+                for (int c = (wl - cbase) & 1; c < nchunks; c += 2) {
+                    const int q = (cbase + c) & 3;
+                    const int n = len - c * C < C ? len - c * C : C;
+                    const uint32_t cn = q < 2 ? cnt0 : cnt1;
+                    const int ngroups = (n + G - 1) / G;
+                    for (int gi = 0; gi < ngroups; ++gi) {
+                        const uint32_t cg = cn + gi;
+                        if (cg >= NA) mbar_wait(bar(Plan::kBarFree + q * NA + static_cast<int>(cg % NA)), ((cg / NA) - 1) & 1, flags);
+                    }
+                    for (int pc = lane; pc < n * ppt; pc += 32) {
+                        const int i = pc / ppt, rem = pc - i * ppt, row = rem >> 2, kc = rem & 3;
+                        const int sl = q * NA + static_cast<int>((cn + i / G) % NA);
+                        cp_async16(x_addr + sl * Plan::kXStage + kc * (NMMA * 16) + row * 16,
+                                   x + static_cast<long long>(row) * p.K + 32 * (kt0 + c * C + i) + 8 * kc);
+                    }
+                    cp_async_commit();
+                    pend_q[npend] = q; pend_cn[npend] = cn; pend_ng[npend] = ngroups;
+                    ++npend;
+                    if (q < 2) cnt0 += ngroups; else cnt1 += ngroups;
+                    if (npend == 2) {
+                        cp_async_wait<1>();
+                        retire();
+                    }
                 }
-                cp_async_commit();
-                pend[npend++] = xi;
-                if (npend == 3) {
-                    cp_async_wait<2>();
-                    retire();
-                }
-                xi += kULoadWarps;
-                more = skip(kULoadWarps);
             }
             while (npend > 0) {
-                if (npend == 3) cp_async_wait<2>(); else if (npend == 2) cp_async_wait<1>(); else cp_async_wait<0>();
+                cp_async_wait<0>();
                 retire();
             }
         }
@@ -627,7 +721,38 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p) 
 
     tc_fence_before();
     __syncthreads();
+    if (tid == 0) DMM_STAMP(0, 0, 3);
     if (warp == kUMmaWarp) tmem_dealloc(tmem, kUTmemCols);
+}
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point (no link-time libcuda).
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+inline EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = [] {
+        void *ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) != cudaSuccess ||
+            qres != cudaDriverEntryPointSuccess)
+            ptr = nullptr;
+        return reinterpret_cast<EncodeTiledFn>(ptr);
+    }();
+    return fn;
+}
+
+// Tensor map of the tiled code matrix seen as uint32 [strips][K/32 * 32], box = c_tiles k-tiles x 4 strips.
+inline int make_codes_map(CUtensorMap *map, const void *codes, long long N, long long K, int c_tiles) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (fn == nullptr) return cudaErrorNotSupported;
+    const cuuint64_t gdim[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(N / 16)};  // K/32 tiles x 32 words
+    const cuuint64_t gstride[1] = {static_cast<cuuint64_t>(K) * 4};                               // bytes per strip
+    const cuuint32_t box[2] = {static_cast<cuuint32_t>(c_tiles * 32), 4};
+    const cuuint32_t estride[2] = {1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void *>(codes), gdim, gstride, box, estride,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : cudaErrorInvalidValue;
 }
 
 template <class Pol, int NMMA>
@@ -641,7 +766,13 @@ inline int launch_umma_one(const UmmaParams &p_in, int num_sms, bool pdl, cudaSt
     if (err != cudaSuccess) return err;
     const long long KT = p.K / 32, NS = p.N / 16, SST = (NS + 15) / 16;
     const long long T = SST * KT;
+    if (T >= (1ll << 31)) return DMM_ERR_SHAPE;
     const unsigned grid = static_cast<unsigned>(T < num_sms ? T : num_sms);
+    p.part.a = static_cast<int>(T / grid);
+    p.part.b = static_cast<int>(T % grid);
+    CUtensorMap map;
+    const int rc = make_codes_map(&map, p.codes, p.N, p.K, Pol::kC);
+    if (rc) return rc;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(kUThreads);
@@ -652,7 +783,7 @@ inline int launch_umma_one(const UmmaParams &p_in, int num_sms, bool pdl, cudaSt
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, kernel, p);
+    return cudaLaunchKernelEx(&cfg, kernel, p, map);
 }
 
 // f8 != 0: PolF8 (needs M <= 8); else PolF16 with M <= 64.

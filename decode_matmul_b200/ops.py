@@ -66,7 +66,7 @@ def decode_matmul_i8(x, weights_compressed, codebook_abs, output=None, *, sign_c
 
 def decode_matmul_fp16(x, weights_compressed, codebook_fp16, scale=1.0, output=None, *,
                        sign_convention=_lib.SIGN_SLOW, layout=_lib.LAYOUT_TILE, path=_lib.PATH_AUTO,
-                       accumulate=False, pdl=False):
+                       accumulate=False, pdl=False, atomic=False):
     """fp32 [M, N] = scale * x (fp16 [M, K]) . W^T with W = decode(codes) / 4, fp32 accumulation.
     ``codebook_fp16`` is fp16 [256, 8] whose entries are odd multiples of 1/2."""
     _check_input(x, "x", torch.float16)
@@ -84,7 +84,9 @@ def decode_matmul_fp16(x, weights_compressed, codebook_fp16, scale=1.0, output=N
         else:
             _check_input(output, "output", torch.float32)
             _req(tuple(output.shape) == (M, N), "output must have shape [M, N]")
-        flags = (_lib.FLAG_ACCUMULATE if accumulate else 0) | (_lib.FLAG_PDL if pdl else 0)
+        _req(not atomic or accumulate, "atomic reduction adds into output: pass accumulate=True (and zero it first)")
+        flags = ((_lib.FLAG_ACCUMULATE if accumulate else 0) | (_lib.FLAG_PDL if pdl else 0)
+                 | (_lib.FLAG_ATOMIC if atomic else 0))
         rc = _lib.lib().dmm_f16(_ptr(x), _ptr(weights_compressed), _ptr(codebook_fp16), float(scale), _ptr(output),
                                 M, N, K, sign_convention, layout, path, flags, None, 0, _stream_ptr(x.device))
     _lib.check(rc, "decode_matmul_fp16")

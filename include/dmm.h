@@ -60,6 +60,11 @@ extern "C" {
                                   weight prefetch may overlap the tail of the previous kernel
                                   in the stream; activations are read only after it finished */
 
+#define DMM_FLAG_ATOMIC 4u     /* tcgen05 paths: out += result by floating-point atomic adds (implies
+                                  accumulate; zero `out` first for a plain product).  Saves the
+                                  workspace round trip of partial sums at the end of the kernel; the
+                                  summation order, hence the last bits of the result, is not fixed */
+
 /* bits of the device status word */
 #define DMM_STATUS_WAIT_TIMEOUT 1u /* a bounded device-side wait expired */
 #define DMM_STATUS_BAD_CODEBOOK 2u /* codebook byte not congruent to 2 mod 4, or fp16 entry not k/4 */

@@ -270,10 +270,14 @@ def run_ours(args):
     xs = {k: torch.randn(B, lin.in_features, device=dev, dtype=torch.float16) for k, lin in stack.layers[0].items()}
     outs = {k: torch.empty(B, lin.out_features, device=dev, dtype=torch.float32) for k, lin in stack.layers[0].items()}
 
-    def kernels_only():
+    def kernels_only():  # same launch mode as the step: PDL chain, atomic accumulation for small batch
         for blk in stack.layers:
             for k, lin in blk.items():
-                lin(xs[k], out=outs[k])
+                if B <= 8:
+                    dmm.decode_matmul_fp16(xs[k], lin.codes, lin.codebook, lin.scale, outs[k], accumulate=True,
+                                           atomic=True, pdl=True)
+                else:
+                    lin(xs[k], out=outs[k])
 
     with torch.cuda.stream(stream):
         kernels_only()

@@ -13,10 +13,11 @@ SIGN_SLOW, SIGN_FAST = 0, 1
 LAYOUT_TILE, LAYOUT_FAST = 0, 1
 PATH_AUTO, PATH_GEMV, PATH_TCGEN05, PATH_TCGEN05_F8 = 0, 1, 2, 3
 FLAG_ACCUMULATE, FLAG_PDL, FLAG_ATOMIC = 1, 2, 4
+X_F16, X_F32, X_F32_SILU_MUL = 0, 1, 2
 STATUS_WAIT_TIMEOUT, STATUS_BAD_CODEBOOK, STATUS_BAD_SMEM = 1, 2, 4
 
 EXPORTS = (
-    "dmm_i8", "dmm_f16", "dmm_f16_noalloc", "dmm_decode", "dmm_workspace_bytes", "dmm_status", "dmm_select_path",
+    "dmm_i8", "dmm_f16", "dmm_f16_fused", "dmm_f16_noalloc", "dmm_decode", "dmm_workspace_bytes", "dmm_status", "dmm_select_path",
     "dmm_launch_count", "dmm_error_string", "dmm_version",
 )
 
@@ -39,6 +40,9 @@ def lib() -> ctypes.CDLL:
     L.dmm_i8.restype = ci
     L.dmm_f16.argtypes = [vp, vp, vp, ctypes.c_float, vp, i64, i64, i64, ci, ci, ci, cu, vp, sz, vp]
     L.dmm_f16.restype = ci
+    L.dmm_f16_fused.argtypes = [vp, ci, i64, i64, vp, vp, ctypes.c_float, vp, i64, i64, i64, ci, ci, ci, cu, vp, i64, vp, sz,
+                                vp]
+    L.dmm_f16_fused.restype = ci
     L.dmm_f16_noalloc.argtypes = [vp, vp, vp, ctypes.c_float, vp, i64, i64, i64, ci, cu, vp]
     L.dmm_f16_noalloc.restype = ci
     L.dmm_decode.argtypes = [vp, vp, ci, vp, i64, i64, ci, ci, vp]

@@ -136,9 +136,10 @@ static long long *g_trace = nullptr;  // device buffer for clock stamps (debug b
 #endif
 
 // tcgen05 path: one launch per chunk of 64 batch columns (8 for the fp6/fp8 operand policy).
-static int run_umma(bool f8, const void *x, const void *codes, const void *cb16, float scale, float *out, long long M,
-                    long long N, long long K, int sign_convention, unsigned flags, void *workspace,
-                    size_t workspace_bytes, cudaStream_t stream) {
+static int run_umma(bool f8, const void *x, int x_kind, long long x_ld, long long x_gap, const void *codes,
+                    const void *cb16, float scale, float *out, long long M, long long N, long long K,
+                    int sign_convention, unsigned flags, void *workspace, size_t workspace_bytes, cudaStream_t stream,
+                    float *zero_ptr = nullptr, long long zero_count = 0) {
     DeviceState *d = nullptr;
     int rc = current_device_state(&d);
     if (rc) return rc;
@@ -148,7 +149,10 @@ static int run_umma(bool f8, const void *x, const void *codes, const void *cb16,
     const long long step = f8 ? 8 : 64;
     for (long long m0 = 0; m0 < M; m0 += step) {
         UmmaParams p = {};
-        p.x = reinterpret_cast<const uint8_t *>(x) + static_cast<size_t>(m0) * K * 2;
+        p.x = reinterpret_cast<const uint8_t *>(x) + static_cast<size_t>(m0) * x_ld * (x_kind == DMM_X_F16 ? 2 : 4);
+        p.x_mode = x_kind;
+        p.x_ld = x_ld;
+        p.x_gap = x_gap;
         p.codes = codes;
         p.cb = cb16;
         p.out = out + static_cast<size_t>(m0) * N;
@@ -162,6 +166,10 @@ static int run_umma(bool f8, const void *x, const void *codes, const void *cb16,
         p.accumulate = (flags & DMM_FLAG_ACCUMULATE) ? 1 : 0;
         p.atomic_reduce = (flags & DMM_FLAG_ATOMIC) ? 1 : 0;
         p.sign_convention = sign_convention;
+        if (m0 == 0) {
+            p.zero_ptr = zero_ptr;
+            p.zero_count = zero_count;
+        }
 #ifdef DMM_TRACE
         p.trace = g_trace;
 #endif
@@ -219,21 +227,38 @@ int dmm_i8(const int8_t *x, const int16_t *codes, const int64_t *cb64, int32_t *
                       static_cast<cudaStream_t>(stream));
 }
 
-int dmm_f16(const void *x, const int16_t *codes, const void *cb16, float scale, float *out, int64_t M, int64_t N,
-            int64_t K, int sign_convention, int layout, int path, unsigned flags, void *workspace,
-            size_t workspace_bytes, void *stream) {
+int dmm_f16_fused(const void *x, int x_kind, int64_t x_ld, int64_t x_gap, const int16_t *codes, const void *cb16,
+                  float scale, float *out, int64_t M, int64_t N, int64_t K, int sign_convention, int layout, int path,
+                  unsigned flags, float *zero_ptr, int64_t zero_count, void *workspace, size_t workspace_bytes,
+                  void *stream) {
     int rc = check_common(x, codes, cb16, out, M, N, K, sign_convention, layout);
     if (rc) return rc;
     if (path != DMM_PATH_AUTO && path != DMM_PATH_GEMV && path != DMM_PATH_TCGEN05 && path != DMM_PATH_TCGEN05_F8)
         return DMM_ERR_ARG;
+    if (x_kind != DMM_X_F16 && x_kind != DMM_X_F32 && x_kind != DMM_X_F32_SILU_MUL) return DMM_ERR_ARG;
+    if (x_ld < K || x_ld % 8 != 0 || x_gap % 4 != 0 || (x_kind == DMM_X_F32_SILU_MUL && x_gap + K > x_ld))
+        return DMM_ERR_SHAPE;
     if (layout != DMM_LAYOUT_TILE) return DMM_ERR_UNSUPPORTED;
-    if (path == DMM_PATH_AUTO) path = dmm_select_path(M, N, K);
+    if (zero_count < 0 || (zero_count > 0 && zero_ptr == nullptr)) return DMM_ERR_ARG;
+    if (path == DMM_PATH_AUTO) path = x_kind == DMM_X_F16 ? dmm_select_path(M, N, K) : DMM_PATH_TCGEN05_F8;
+    if (zero_count > 0 && path != DMM_PATH_TCGEN05 && path != DMM_PATH_TCGEN05_F8) return DMM_ERR_UNSUPPORTED;
+    // fp32 inputs are converted by the loaders of the fp8-operand kernel only
+    if (x_kind != DMM_X_F16 && path != DMM_PATH_TCGEN05_F8) return DMM_ERR_UNSUPPORTED;
     if (path == DMM_PATH_TCGEN05 || path == DMM_PATH_TCGEN05_F8)
-        return run_umma(path == DMM_PATH_TCGEN05_F8, x, codes, cb16, scale, out, M, N, K, sign_convention, flags,
-                        workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
-    // the kernels accumulate quarter units: fold the 1/4 into the scale
+        return run_umma(path == DMM_PATH_TCGEN05_F8, x, x_kind, x_ld, x_gap, codes, cb16, scale, out, M, N, K,
+                        sign_convention, flags, workspace, workspace_bytes, static_cast<cudaStream_t>(stream), zero_ptr,
+                        zero_count);
+    if (x_ld != K) return DMM_ERR_UNSUPPORTED;
+    // the streaming kernel accumulates quarter units: fold the 1/4 into the scale
     return run_stream(1, x, codes, cb16, 1, 0.25f * scale, out, M, N, K, sign_convention, flags, workspace,
                       workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+int dmm_f16(const void *x, const int16_t *codes, const void *cb16, float scale, float *out, int64_t M, int64_t N,
+            int64_t K, int sign_convention, int layout, int path, unsigned flags, void *workspace,
+            size_t workspace_bytes, void *stream) {
+    return dmm_f16_fused(x, DMM_X_F16, K, 0, codes, cb16, scale, out, M, N, K, sign_convention, layout, path, flags,
+                         nullptr, 0, workspace, workspace_bytes, stream);
 }
 
 int dmm_f16_noalloc(const void *x, const int16_t *codes, const void *cb16, float scale, float *out, int64_t M,
@@ -255,6 +280,8 @@ int dmm_f16_noalloc(const void *x, const int16_t *codes, const void *cb16, float
     if (err != cudaSuccess) return err;
     UmmaParams p = {};
     p.x = x;
+    p.x_mode = DMM_X_F16;
+    p.x_ld = K;
     p.codes = codes;
     p.cb = cb16;
     p.out = out;

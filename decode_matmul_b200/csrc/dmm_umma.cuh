@@ -57,6 +57,14 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
+// One lane of the (converged) warp: true in exactly one thread.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile(
+        "{\n.reg .b32 rx;\n.reg .pred px;\nelect.sync rx|px, 0xffffffff;\nselp.u32 %0, 1, 0, px;\n}\n"
+        : "=r"(pred));
+    return pred != 0;
+}
 __device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr), "r"(r[0]),
                  "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
@@ -159,9 +167,13 @@ struct UmmaPlan {
     static constexpr uint32_t kBufCols = 2 * Pol::kG * Pol::kACols;  // one group buffer: [tile][k-tile][cols]
     static constexpr uint32_t kACols = 4 * Pol::kNA * kBufCols;
     static_assert(kDCols + kACols <= kUTmemCols, "TMEM plan exceeds 512 columns");
-    static constexpr int kSlots = 4 * Pol::kNA;                   // group buffers = activation stages
+    static constexpr int kSlots = 4 * Pol::kNA;                   // group buffers (= fp16 activation stages)
     static constexpr uint32_t kXStage = Pol::kG * Pol::x_tile_bytes(NMMA);
-    static constexpr uint32_t kXBytes = kSlots * kXStage;
+    // fp8 policy: the activation planes of a whole run of k-tiles ("epoch") stay resident in one
+    // of kEpochs buffers, densely packed [tile][k-half][plane][row < M][16 B]
+    static constexpr int kEpochs = 4;
+    static constexpr uint32_t kEpochBytes = 14336;
+    static constexpr uint32_t kXBytes = Pol::kIsF8 ? kEpochs * kEpochBytes + 256 : kSlots * kXStage;
     static constexpr int kNB = Pol::out_cols(NMMA);               // output columns per launch
     static constexpr uint32_t kPreBytes = kUBarBytes + kXBytes;
     static constexpr uint32_t kSlotBytes = 4 * Pol::kC * 128;     // ring slot: 4 strips x C k-tiles
@@ -175,25 +187,35 @@ struct UmmaPlan {
     static constexpr int kBarCode = 0;                                   // [16][kRing]  TMA completion
     static constexpr int kBarFull = kBarCode + kUDecWarps * Pol::kRing;  // [kSlots] 4 decoder warps + 1 loader
     static constexpr int kBarFree = kBarFull + kSlots;                   // [kSlots] tcgen05.commit
-    static constexpr int kBarDReady = kBarFree + kSlots;
+    static constexpr int kBarXReady = kBarFree + kSlots;                 // [kEpochs] loader warps
+    static constexpr int kBarXFree = kBarXReady + kEpochs;               // [kEpochs] both issuers (commit)
+    static constexpr int kBarDReady = kBarXFree + kEpochs;
     static constexpr int kBarDFree = kBarDReady + 1;
     static constexpr int kBarCount = kBarDFree + 1;
     static_assert(kBarCount * 8 + 64 <= kUBarBytes, "barrier block too small");
 };
 
+// How the activation loaders read their input (fp8 policy): plain fp16, or fp32 produced by
+// the previous layer and converted on the fly, optionally through silu(a) * b of two halves.
+constexpr int kXHalf = 0, kXFloat = 1, kXSiluMul = 2;
+
 struct UmmaParams {
-    const void *x;       // [M, K] fp16
+    const void *x;       // x_mode 0: fp16 [M, K]; 1: fp32 [M, x_ld]; 2: fp32 [M, x_ld], gate at k, up at x_gap + k
     const void *codes;   // tiled codes
     const void *cb;      // fp16 [256, 8]
     float *out;          // [M, N]
     float *partials;     // workspace [grid][2][kPartial]
     unsigned *tickets;   // workspace, one per super-tile, zero between launches
     long long M, N, K;
+    int x_mode;
+    long long x_ld, x_gap;  // row stride of x in elements; offset of the second operand (mode 2)
     float scale;         // includes the unit of the accumulators (1/4 for q, 2 for q/8)
     int accumulate;
     int atomic_reduce;   // partial super-tiles are added to `out` with red.global.add (out must hold the
                          // value to add to): no workspace round trip, summation order not fixed
     int sign_convention;
+    float *zero_ptr;     // optional: buffer this kernel clears on its way (see dmm_f16_fused)
+    long long zero_count;
     Part32 part;         // tiles per CTA: part.a = T / grid, part.b = T % grid
     unsigned dyn_smem_bytes;
     long long *trace;    // debugging aid (builds with -DDMM_TRACE only): clock stamps of CTA 0
@@ -256,7 +278,9 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
     // ---- set-up: barriers, TMEM, zeroed activation stages ----
     if (tid < Plan::kBarCount) {
         uint32_t count = 1;                                                  // TMA, tcgen05.commit
-        if (tid >= Plan::kBarFull && tid < Plan::kBarFree) count = 5;         // 4 decoder warps + loader
+        if (tid >= Plan::kBarFull && tid < Plan::kBarFree) count = Pol::kIsF8 ? 4 : 5;  // decoder warps (+ loader)
+        if (tid >= Plan::kBarXReady && tid < Plan::kBarXFree) count = kULoadWarps;
+        if (tid >= Plan::kBarXFree && tid < Plan::kBarDReady) count = NACC;
         if (tid == Plan::kBarDReady) count = NACC;
         if (tid == Plan::kBarDFree) count = 8;
         mbar_init(bar(tid), count);
@@ -316,7 +340,7 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
         ccur = icur;
         int iidx = 0, cidx = 0;
         if (tid == 0) DMM_STAMP(0, 3, 1);
-        while (iidx < RING && icur.ok) {  // weights do not depend on the previous kernel
+        if (icur.ok) {  // first chunk now (weights do not depend on the previous kernel) ...
             issue(icur, iidx);
             if (tid == 0) DMM_STAMP(0, 3, 2);
             icur.c += 4;
@@ -328,10 +352,22 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
         const bool bad = lut_fill(lut_addr, p.cb, 1, p.sign_convention, Pol::kFmt, tid, kUDecWarps * 32, Pol::kIsF8 != 0);
         if (bad) raise_status(DMM_STATUS_BAD_CODEBOOK);
         if (tid == 0) DMM_STAMP(0, 1, 1);
+        if (lane == 0) DMM_STAMP(0, 8 + warp, 0);
         named_barrier(1, kUDecWarps * 32);
+        while (iidx < RING && icur.ok) {  // ... the rest of the ring once the table is built
+            issue(icur, iidx);
+            icur.c += 4;
+            settle(icur);
+            ++iidx;
+        }
         const LutLane ll = lut_lane(lut_addr, lane, Pol::kIsF8 != 0);
         grid_dep_wait();
         if (tid == 0) DMM_STAMP(0, 0, 2);
+        if (p.zero_ptr != nullptr) {  // a later kernel will accumulate into it
+            for (long long i = static_cast<long long>(cta) * (kUDecWarps * 32) + tid; i < p.zero_count;
+                 i += static_cast<long long>(gridDim.x) * (kUDecWarps * 32))
+                p.zero_ptr[i] = 0.f;
+        }
 
         const uint32_t tlane = tmem + (static_cast<uint32_t>(wq * 32) << 16);
         uint32_t sA = 0;  // groups this decoder group has produced
@@ -341,7 +377,9 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
                 const int len = seg_len(ss);
                 const int n = len - ccur.c * C < C ? len - ccur.c * C : C;  // k-tiles in this chunk
                 const int slot = cidx % RING;
+                if (tid == 0) DMM_STAMP(5, cidx, 0);
                 mbar_wait(bar(Plan::kBarCode + warp * RING + slot), static_cast<uint32_t>((cidx / RING) & 1), flags);
+                if (tid == 0) DMM_STAMP(5, cidx, 1);
                 const uint32_t src = wring + slot * Plan::kSlotBytes + (lane >> 3) * (C * 128) + (lane & 7) * 16;
 #pragma unroll 1
                 for (int g0 = 0; g0 < n; g0 += G) {
@@ -397,12 +435,14 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
                     ++sA;
                 }
                 __syncwarp();  // every lane has read the slot: refill it
+                if (tid == 0) DMM_STAMP(5, cidx, 2);
                 if (icur.ok) {
                     issue(icur, iidx);
                     icur.c += 4;
                     settle(icur);
                     ++iidx;
                 }
+                if (tid == 0) DMM_STAMP(5, cidx, 3);
                 ccur.c += 4;
                 settle(ccur);
                 ++cidx;
@@ -524,17 +564,33 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
     } else if (warp < kUMmaWarp + kUMmaWarps) {
         // =============================== MMA issuers ===============================
         // issuer `me` serves decoder groups q with (q & 1) == me and owns accumulator `me`
+        // The whole warp runs the loop converged (so that addresses and descriptors stay in
+        // uniform registers); one elected lane issues the tcgen05 instructions.
         const int me = warp - kUMmaWarp;
-        if (lane == 0) {
+        {
+            const bool leader = elect_one();
             uint32_t cnt0 = 0, cnt1 = 0;  // groups consumed from decoder groups me and me + 2
             int segidx = 0;
             const uint32_t idesc = Pol::kIsF8
                                        ? ((1u << 4) | (3u << 7) | (1u << 10) | ((NMMA >> 3) << 17) | ((128u >> 4) << 24))
                                        : ((1u << 4) | ((NMMA >> 3) << 17) | ((128u >> 4) << 24));
             // descriptor of activation stage 0; later stages and k-halves only move the address field
-            const uint64_t xdesc0 = Pol::kIsF8 ? smem_desc(x_addr, 512, 128) : smem_desc(x_addr, NMMA * 16, 128);
-            int cbase = 0;
-            for (int ss = ss_first; ss <= ss_last; cbase += seg_chunks(ss), ++ss, ++segidx) {
+            const uint32_t tile_b = 128u * static_cast<uint32_t>(p.M);  // fp8: bytes of one k-tile of planes
+            const int E = static_cast<int>((Plan::kEpochBytes / tile_b) & ~1u);  // k-tiles per epoch
+            const uint64_t xdesc0 = Pol::kIsF8 ? smem_desc(x_addr, tile_b / 2, tile_b / 8) : smem_desc(x_addr, NMMA * 16, 128);
+            int cur_ep = -1, ep_end = 0;  // fp8: epoch whose buffer is being read; first tile past it
+            uint32_t ep_addr = 0;
+            auto enter_epoch = [&](int e) {
+                // every earlier epoch is finished for this issuer: let the loaders reuse its buffer
+                for (int r = cur_ep < 0 ? 0 : cur_ep; r < e; ++r)
+                    if (leader) tc_commit(bar(Plan::kBarXFree + r % Plan::kEpochs));
+                mbar_wait(bar(Plan::kBarXReady + e % Plan::kEpochs), static_cast<uint32_t>((e / Plan::kEpochs) & 1), flags);
+                cur_ep = e;
+                ep_end = (e + 1) * E;
+                ep_addr = ((e % Plan::kEpochs) * Plan::kEpochBytes) >> 4;
+            };
+            int cbase = 0, jseg = 0;  // chunks / k-tiles of earlier segments
+            for (int ss = ss_first; ss <= ss_last; cbase += seg_chunks(ss), jseg += seg_len(ss), ++ss, ++segidx) {
                 const int len = seg_len(ss);
                 const int nchunks = (len + C - 1) / C;
                 if (segidx > 0) {
@@ -549,36 +605,52 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
                     for (int g0 = 0; g0 < n; g0 += G) {
                         const uint32_t cn = q < 2 ? cnt0 : cnt1;
                         const int sl = q * NA + static_cast<int>(cn % NA);
-                        if (me == 0) DMM_STAMP(2, cn, 0);
+                        if (me == 0 && leader) DMM_STAMP(2, cn, 0);
                         mbar_wait(bar(Plan::kBarFull + sl), (cn / NA) & 1, flags);
                         tc_fence_after();
-                        if (me == 0) DMM_STAMP(2, cn, 1);
+                        if (me == 0 && leader) DMM_STAMP(2, cn, 1);
                         const uint64_t xd = xdesc0 + ((static_cast<uint32_t>(sl) * Plan::kXStage) >> 4);
                         const uint32_t a_col = tmem + Plan::kDCols + static_cast<uint32_t>(sl) * Plan::kBufCols;
+                        if constexpr (Pol::kIsF8) {
+                            // tile by tile (both MMA tiles of a k-tile back to back), so that an
+                            // epoch is only left when nothing issued later still reads its buffer
 #pragma unroll
-                        for (int t = 0; t < 2; ++t) {
-                            const uint32_t d_col = tmem + static_cast<uint32_t>((t * NACC + me) * NMMA);
-                            uint32_t acc = first ? 0u : 1u;
-                            if constexpr (Pol::kIsF8) {
+                            for (int i = 0; i < G; ++i) {
+                                if (g0 + i < n) {
+                                    const int jt = jseg + c * C + g0 + i;  // CTA-wide k-tile index
+                                    if (jt >= ep_end) enter_epoch(jt / E);
+                                    const uint64_t xt = xdesc0 + ep_addr + ((static_cast<uint32_t>(jt - (ep_end - E)) * tile_b) >> 4);
+                                    const uint32_t acc = (first && i == 0) ? 0u : 1u;
+                                    if (leader) {
 #pragma unroll
-                                for (int i = 0; i < G; ++i) {
-                                    if (g0 + i < n) {
-                                        mma_ts_f8(d_col, a_col + (t * G + i) * Pol::kACols, xd + ((i * 1024u) >> 4), idesc, acc);
-                                        acc = 1u;
+                                        for (int t = 0; t < 2; ++t)
+                                            mma_ts_f8(tmem + static_cast<uint32_t>((t * NACC + me) * NMMA),
+                                                      a_col + (t * G + i) * Pol::kACols, xt, idesc, acc);
                                     }
                                 }
-                            } else {
-                                mma_ts_f16(d_col, a_col + t * G * Pol::kACols, xd, idesc, acc);
-                                mma_ts_f16(d_col, a_col + t * G * Pol::kACols + 8, xd + ((2 * NMMA * 16) >> 4), idesc, 1u);
+                            }
+                        } else {
+#pragma unroll
+                            for (int t = 0; t < 2; ++t) {
+                                const uint32_t d_col = tmem + static_cast<uint32_t>((t * NACC + me) * NMMA);
+                                if (leader) {
+                                    mma_ts_f16(d_col, a_col + t * G * Pol::kACols, xd, idesc, first ? 0u : 1u);
+                                    mma_ts_f16(d_col, a_col + t * G * Pol::kACols + 8, xd + ((2 * NMMA * 16) >> 4), idesc, 1u);
+                                }
                             }
                         }
                         first = false;
-                        tc_commit(bar(Plan::kBarFree + sl));
-                        if (me == 0) DMM_STAMP(2, cn, 2);
+                        if (leader) tc_commit(bar(Plan::kBarFree + sl));
+                        if (me == 0 && leader) DMM_STAMP(2, cn, 2);
                         if (q < 2) ++cnt0; else ++cnt1;
                     }
                 }
-                tc_commit(bar(Plan::kBarDReady));
+                if (leader) tc_commit(bar(Plan::kBarDReady));
+            }
+            if constexpr (Pol::kIsF8) {
+                const int nep = (i1 - i0 + E - 1) / E;
+                for (int r = cur_ep < 0 ? 0 : cur_ep; r < nep; ++r)
+                    if (leader) tc_commit(bar(Plan::kBarXFree + r % Plan::kEpochs));
             }
         }
     } else {
@@ -593,85 +665,82 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
         int cbase = 0;
 
         if constexpr (Pol::kIsF8) {
-            // a chunk has at most kC * 8 * 4 = 128 pieces: up to four rounds of 32 lanes; the raw
-            // activations of the NEXT chunk are fetched before the current one is converted
-            constexpr int R = 4;
-            uint4 cur[R], nxt[R];
-            // chunk iterator over (segment, chunk of my parity)
-            int ss = ss_first, c = wl & 1;
-            auto settle = [&]() -> bool {
-                while (c * C >= seg_len(ss)) {
-                    if (ss == ss_last) return false;
-                    cbase += seg_chunks(ss);
-                    ++ss;
-                    c = (wl - cbase) & 1;
-                }
-                return true;
-            };
-            auto fetch = [&](uint4(&v)[R], int fss, int fc) {
-                const int len = seg_len(fss);
-                const int n = len - fc * C < C ? len - fc * C : C;
-                const int kt = seg_kt0(fss) + fc * C;
+            // The loaders never touch a barrier per tile: they fill whole epochs of the CTA's
+            // k-tile sequence (segment after segment) with the four E5M2 planes of the activations,
+            // densely packed [tile][k-half][plane][row][16 B]; the issuers point their operand
+            // descriptors straight into these buffers.  A piece is 8 consecutive k of one row.
+            constexpr int U = 4;  // pieces in flight per thread
+            const uint32_t tile_b = 128u * static_cast<uint32_t>(M);
+            const int E = static_cast<int>((Plan::kEpochBytes / tile_b) & ~1u);
+            const int ntiles = i1 - i0;
+            const int nep = (ntiles + E - 1) / E;
+            const int lt = wl * 32 + lane;
+            constexpr int LT = kULoadWarps * 32;
+            const float *xf = reinterpret_cast<const float *>(p.x);
+            for (int e = 0; e < nep; ++e) {
+                if (wl == 0 && lane == 0) DMM_STAMP(3, e, 0);
+                if (e >= Plan::kEpochs)
+                    mbar_wait(bar(Plan::kBarXFree + e % Plan::kEpochs), static_cast<uint32_t>(((e / Plan::kEpochs) - 1) & 1), flags);
+                const int t_lo = e * E;
+                const int nt = ntiles - t_lo < E ? ntiles - t_lo : E;
+                const int npieces = nt * ppt;
+                const uint32_t ebuf = x_addr + (e % Plan::kEpochs) * Plan::kEpochBytes;
+                for (int pbase = 0; pbase < npieces; pbase += LT * U) {
+                    uint32_t h[U][4];
+                    uint32_t dst[U];
 #pragma unroll
-                for (int r = 0; r < R; ++r) {
-                    const int pc = lane + 32 * r;
-                    if (pc < n * ppt) {
-                        const int i = pc / ppt, rem = pc - i * ppt, row = rem >> 2, kc = rem & 3;
-                        v[r] = __ldg(reinterpret_cast<const uint4 *>(x + static_cast<long long>(row) * p.K + 32 * (kt + i) + 8 * kc));
+                    for (int u = 0; u < U; ++u) {
+                        const int pc = pbase + u * LT + lt;
+                        dst[u] = 0;
+                        if (pc < npieces) {
+                            const int jl = pc / ppt, rem = pc - jl * ppt, row = rem >> 2, kc = rem & 3;
+                            const int gt = i0 + t_lo + jl;          // global tile index -> k-tile
+                            const int kt = gt - (gt / KT) * KT;
+                            const long long k0 = 32ll * kt + 8 * kc;
+                            dst[u] = ebuf + jl * tile_b + (kc >> 1) * (tile_b / 2) + row * 16 + (kc & 1) * 8;
+                            if (p.x_mode == kXHalf) {
+                                const uint4 v = __ldg(reinterpret_cast<const uint4 *>(x + row * p.x_ld + k0));
+                                h[u][0] = v.x; h[u][1] = v.y; h[u][2] = v.z; h[u][3] = v.w;
+                            } else {
+                                const float4 a0 = __ldcg(reinterpret_cast<const float4 *>(xf + row * p.x_ld + k0));
+                                const float4 a1 = __ldcg(reinterpret_cast<const float4 *>(xf + row * p.x_ld + k0 + 4));
+                                float f[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+                                if (p.x_mode == kXSiluMul) {
+                                    const float4 b0 = __ldcg(reinterpret_cast<const float4 *>(xf + row * p.x_ld + p.x_gap + k0));
+                                    const float4 b1 = __ldcg(reinterpret_cast<const float4 *>(xf + row * p.x_ld + p.x_gap + k0 + 4));
+                                    const float g[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+                                    for (int j = 0; j < 8; ++j) f[j] = f[j] / (1.0f + __expf(-f[j])) * g[j];
+                                }
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    const __half2 hh = __floats2half2_rn(f[2 * j], f[2 * j + 1]);
+                                    h[u][j] = *reinterpret_cast<const uint32_t *>(&hh);
+                                }
+                            }
+                        }
                     }
-                }
-            };
-            bool ok = settle();
-            if (ok) fetch(cur, ss, c);
-            uint32_t pass = 0;
-            while (ok) {
-                const int my_ss = ss, my_c = c, my_cbase = cbase;
-                // look ahead: next chunk of my parity
-                c += 2;
-                const bool more = settle();
-                if (more) fetch(nxt, ss, c);
-                if (wl == 0 && lane == 0) DMM_STAMP(3, pass, 0);
-
-                const int len = seg_len(my_ss);
-                const int n = len - my_c * C < C ? len - my_c * C : C;
-                const int q = (my_cbase + my_c) & 3;
-                const uint32_t cn = q < 2 ? cnt0 : cnt1;
-                const int ngroups = (n + G - 1) / G;
-                for (int gi = 0; gi < ngroups; ++gi) {
-                    const uint32_t cg = cn + gi;
-                    if (cg >= NA) mbar_wait(bar(Plan::kBarFree + q * NA + static_cast<int>(cg % NA)), ((cg / NA) - 1) & 1, flags);
-                }
 #pragma unroll
-                for (int r = 0; r < R; ++r) {
-                    const int pc = lane + 32 * r;
-                    if (pc < n * ppt) {
-                        const int i = pc / ppt, rem = pc - i * ppt, row = rem >> 2, kc = rem & 3;
-                        const int sl = q * NA + static_cast<int>((cn + i / G) % NA);
-                        uint32_t h[4] = {cur[r].x, cur[r].y, cur[r].z, cur[r].w};
-                        // tile layout [k-half][8*plane + row][16 B]
-                        const uint32_t dst = x_addr + sl * Plan::kXStage + (i % G) * 1024 + (kc >> 1) * 512 + row * 16 + (kc & 1) * 8;
+                    for (int u = 0; u < U; ++u) {
+                        if (dst[u] != 0) {
 #pragma unroll
-                        for (int pl = 0; pl < 4; ++pl) {
-                            // plane pl = top byte of each half (an E5M2 number), then subtract it
-                            sts64(dst + pl * 128, prmt(h[0], h[1], 0x7531u), prmt(h[2], h[3], 0x7531u));
+                            for (int pl = 0; pl < 4; ++pl) {
+                                // plane pl = top byte of each half (an E5M2 number), then subtract it
+                                sts64(dst[u] + pl * (tile_b / 8), prmt(h[u][0], h[u][1], 0x7531u), prmt(h[u][2], h[u][3], 0x7531u));
 #pragma unroll
-                            for (int e = 0; e < 4; ++e) {
-                                const uint32_t top = h[e] & 0xFF00FF00u;
-                                __half2 rr = __hsub2(*reinterpret_cast<__half2 *>(&h[e]), *reinterpret_cast<const __half2 *>(&top));
-                                h[e] = *reinterpret_cast<uint32_t *>(&rr);
+                                for (int j = 0; j < 4; ++j) {
+                                    const uint32_t top = h[u][j] & 0xFF00FF00u;
+                                    __half2 rr = __hsub2(*reinterpret_cast<__half2 *>(&h[u][j]), *reinterpret_cast<const __half2 *>(&top));
+                                    h[u][j] = *reinterpret_cast<uint32_t *>(&rr);
+                                }
                             }
                         }
                     }
                 }
                 fence_async_smem();
                 __syncwarp();
-                if (lane < ngroups) mbar_arrive(bar(Plan::kBarFull + q * NA + static_cast<int>((cn + lane) % NA)));
-                if (wl == 0 && lane == 0) DMM_STAMP(3, pass, 1);
-                if (q < 2) cnt0 += ngroups; else cnt1 += ngroups;
-#pragma unroll
-                for (int r = 0; r < R; ++r) cur[r] = nxt[r];
-                ok = more;
-                ++pass;
+                if (lane == 0) mbar_arrive(bar(Plan::kBarXReady + e % Plan::kEpochs));
+                if (wl == 0 && lane == 0) DMM_STAMP(3, e, 1);
             }
         } else {
             // fp16 activations: cp.async straight into the stage, two chunks in flight
@@ -700,7 +769,7 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
                         const int i = pc / ppt, rem = pc - i * ppt, row = rem >> 2, kc = rem & 3;
                         const int sl = q * NA + static_cast<int>((cn + i / G) % NA);
                         cp_async16(x_addr + sl * Plan::kXStage + kc * (NMMA * 16) + row * 16,
-                                   x + static_cast<long long>(row) * p.K + 32 * (kt0 + c * C + i) + 8 * kc);
+                                   x + static_cast<long long>(row) * p.x_ld + 32 * (kt0 + c * C + i) + 8 * kc);
                     }
                     cp_async_commit();
                     pend_q[npend] = q; pend_cn[npend] = cn; pend_ng[npend] = ngroups;

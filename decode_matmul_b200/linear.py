@@ -97,8 +97,17 @@ class LinearStack:
         self.code_bytes_total = sum(n * k // 4 for n, k in shapes.values()) * cfg["layers"]
         self.launches_per_step = 4 * cfg["layers"]
 
-    def step(self, h: torch.Tensor, path: int = _lib.PATH_AUTO) -> torch.Tensor:
-        """One pass of the stack over the fp32 residual stream ``h`` [B, hidden] (updated in place)."""
+    def step(self, h: torch.Tensor, path: int = _lib.PATH_AUTO, fused: bool | None = None) -> torch.Tensor:
+        """One pass of the stack over the fp32 residual stream ``h`` [B, hidden] (updated in place).
+
+        ``fused`` (default: whenever the batch is at most 8): every elementwise step between two
+        layers runs inside the matmul kernels -- the loaders read fp32 and round to fp16 or form
+        silu(gate) * up, the epilogues add onto the residual stream with atomic adds, and each
+        kernel clears the buffer a later kernel accumulates into.  Four launches per block."""
+        if fused is None:
+            fused = h.shape[0] <= 8 and path == _lib.PATH_AUTO
+        if fused:
+            return self._step_fused(h)
         hid_loc = self.hidden // self.world
         ffn_loc = self.ffn // self.world
         for blk in self.layers:
@@ -109,6 +118,48 @@ class LinearStack:
             g = blk["gate_up"](h.to(torch.float16), path=path)
             act = (torch.nn.functional.silu(g[:, :ffn_loc]) * g[:, ffn_loc:]).to(torch.float16)
             self._row_parallel(blk["down"], act, h, path)
+        return h
+
+    def _buffers(self, batch: int):
+        key = (batch,)
+        if getattr(self, "_buf_key", None) != key:
+            n_qkv = self.layers[0]["qkv"].out_features
+            n_gu = self.layers[0]["gate_up"].out_features
+            mk = lambda n: torch.zeros((batch, n), dtype=torch.float32, device=self.device)
+            self._buf = {"a": mk(n_qkv), "g": mk(n_gu), "po": mk(self.hidden), "pd": mk(self.hidden)}
+            self._buf_key = key
+        return self._buf
+
+    def _step_fused(self, h: torch.Tensor) -> torch.Tensor:
+        from .ops import decode_matmul_fused as mm
+
+        buf = self._buffers(h.shape[0])
+        a, g, po, pd = buf["a"], buf["g"], buf["po"], buf["pd"]
+        hid_loc, ffn_loc = self.hidden // self.world, self.ffn // self.world
+        tp = self.world > 1
+        # Every output is accumulated with atomic adds, so it has to be zero when its kernel
+        # starts.  Each kernel clears one buffer that is idle while it runs (after it has seen the
+        # previous kernel finish): qkv clears g, o clears pd, gate_up clears a, down clears po.
+        a.zero_()
+        if tp:
+            po.zero_()
+        for blk in self.layers:
+            q, o, gu, dn = blk["qkv"], blk["o"], blk["gate_up"], blk["down"]
+            kw = dict(accumulate=True, atomic=True, pdl=True)
+            mm(h, q.codes, q.codebook, q.scale, a, x_kind=_lib.X_F32, zero=g, **kw)
+            if tp:
+                mm(a, o.codes, o.codebook, o.scale, po, x_kind=_lib.X_F32, zero=pd, **kw)
+                torch.distributed.all_reduce(po, group=self.group)
+                h.add_(po)
+            else:
+                mm(a, o.codes, o.codebook, o.scale, h, x_kind=_lib.X_F32, **kw)
+            mm(h, gu.codes, gu.codebook, gu.scale, g, x_kind=_lib.X_F32, zero=a, **kw)
+            if tp:
+                mm(g, dn.codes, dn.codebook, dn.scale, pd, x_kind=_lib.X_F32_SILU_MUL, x_gap=ffn_loc, zero=po, **kw)
+                torch.distributed.all_reduce(pd, group=self.group)
+                h.add_(pd)
+            else:
+                mm(g, dn.codes, dn.codebook, dn.scale, h, x_kind=_lib.X_F32_SILU_MUL, x_gap=ffn_loc, **kw)
         return h
 
     def _row_parallel(self, lin: DecodeLinear, x16: torch.Tensor, h: torch.Tensor, path: int) -> None:

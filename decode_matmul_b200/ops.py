@@ -93,6 +93,40 @@ def decode_matmul_fp16(x, weights_compressed, codebook_fp16, scale=1.0, output=N
     return output
 
 
+def decode_matmul_fused(x, weights_compressed, codebook_fp16, scale, output, *, x_kind=_lib.X_F32, k=None, x_gap=0,
+                        sign_convention=_lib.SIGN_SLOW, accumulate=False, pdl=False, atomic=False, zero=None):
+    """``decode_matmul_fp16`` reading the previous layer's fp32 output directly.
+
+    ``x`` is fp32 [M, ld] (or fp16 with ``x_kind=X_F16``); the kernel's loaders round it to fp16
+    themselves (``X_F32``) or first form ``silu(x[:, :k]) * x[:, x_gap:x_gap + k]``
+    (``X_F32_SILU_MUL``), so no separate cast / activation kernel runs between two layers.
+    ``k`` is the reduction length (default: the whole row); the result is written or added to
+    ``output`` (fp32 [M, N]).  ``zero``: an fp32 tensor that this kernel clears on its way (the
+    output of a later ``atomic`` call); it must not be an operand of this call or the one before."""
+    _check_input(x, "x", torch.float16 if x_kind == _lib.X_F16 else torch.float32)
+    _check_input(weights_compressed, "weights_compressed", torch.int16)
+    _check_input(codebook_fp16, "codebook_fp16", torch.float16)
+    _check_input(output, "output", torch.float32)
+    _req(x.dim() == 2 and weights_compressed.dim() == 2, "x and weights_compressed must be 2-D")
+    M, ld = x.shape
+    N, K = weights_compressed.size(0), weights_compressed.size(1) * 8
+    _req(k is None or k == K, "k must equal 8 * weights_compressed.size(-1)")
+    _req(ld >= K, "x rows are shorter than the reduction length")
+    _req(tuple(output.shape) == (M, N), "output must have shape [M, N]")
+    _req(not atomic or accumulate, "atomic reduction adds into output: pass accumulate=True")
+    if zero is not None:
+        _check_input(zero, "zero", torch.float32)
+    flags = ((_lib.FLAG_ACCUMULATE if accumulate else 0) | (_lib.FLAG_PDL if pdl else 0)
+             | (_lib.FLAG_ATOMIC if atomic else 0))
+    with torch.cuda.device(x.device):
+        rc = _lib.lib().dmm_f16_fused(_ptr(x), x_kind, ld, x_gap, _ptr(weights_compressed), _ptr(codebook_fp16),
+                                      float(scale), _ptr(output), M, N, K, sign_convention, _lib.LAYOUT_TILE,
+                                      _lib.PATH_AUTO, flags, None if zero is None else _ptr(zero),
+                                      0 if zero is None else zero.numel(), None, 0, _stream_ptr(x.device))
+    _lib.check(rc, "decode_matmul_fused")
+    return output
+
+
 def decode_matmul_fp16_noalloc(x, weights_compressed, codebook_fp16, scale, output, *,
                                sign_convention=_lib.SIGN_SLOW, accumulate=False, pdl=False):
     """``decode_matmul_fp16`` for programs that cannot let the library allocate device memory

@@ -54,6 +54,11 @@ extern "C" {
 #define DMM_PATH_TCGEN05_F8 3 /* tcgen05 + TMEM, weights as fp6 and activations as exact fp8 planes;
                                  the small-batch path, taken per chunk of 8 batch columns */
 
+/* what dmm_f16_fused reads as activations */
+#define DMM_X_F16 0          /* fp16 [M, x_ld] */
+#define DMM_X_F32 1          /* fp32 [M, x_ld], rounded to fp16 on the fly */
+#define DMM_X_F32_SILU_MUL 2 /* fp32 [M, x_ld]: fp16(silu(x[:, k]) * x[:, x_gap + k]) */
+
 /* launch flags (bit mask) */
 #define DMM_FLAG_ACCUMULATE 1u /* out += result instead of out = result */
 #define DMM_FLAG_PDL 2u        /* launch with programmatic stream serialization: the kernel's
@@ -93,6 +98,27 @@ int dmm_i8(const int8_t *x, const int16_t *codes, const int64_t *cb64, int32_t *
 int dmm_f16(const void *x, const int16_t *codes, const void *cb16, float scale, float *out,
             int64_t M, int64_t N, int64_t K, int sign_convention, int layout, int path,
             unsigned flags, void *workspace, size_t workspace_bytes, void *stream);
+
+/*
+ * dmm_f16 with the operator's neighbours folded in (the elementwise steps that sit between two
+ * quantised linear layers and that the reference leaves to the caller): the activation
+ * loaders read the fp32 output of the previous layer and round it to fp16 themselves
+ * (DMM_X_F32), or form silu(gate) * up of a fused gate/up output first (DMM_X_F32_SILU_MUL),
+ * and DMM_FLAG_ACCUMULATE / DMM_FLAG_ATOMIC add the product onto a residual stream.  The
+ * result equals running those steps separately in fp32 and calling dmm_f16.
+ * x_ld = row stride of x in elements (>= K, multiple of 8); x_gap = offset of the second
+ * operand for DMM_X_F32_SILU_MUL.  fp32 inputs take the small-batch tcgen05 path only.
+ * zero_ptr / zero_count (optional): a float buffer that this kernel sets to zero once the
+ * previous kernel of the stream has finished -- the output buffer of a LATER call that runs
+ * with DMM_FLAG_ATOMIC, so that a chain of layers needs no memset between kernels.  The
+ * buffer must not be read or written by this call or by the kernel right before it.
+ * The reference has no counterpart: its operator starts at int8 activations
+ * (decode_matmul_cuda.cu:186).
+ */
+int dmm_f16_fused(const void *x, int x_kind, int64_t x_ld, int64_t x_gap, const int16_t *codes,
+                  const void *cb16, float scale, float *out, int64_t M, int64_t N, int64_t K,
+                  int sign_convention, int layout, int path, unsigned flags, float *zero_ptr,
+                  int64_t zero_count, void *workspace, size_t workspace_bytes, void *stream);
 
 /*
  * dmm_f16 for callers that must not allocate.  (No counterpart in the reference.)

@@ -236,12 +236,12 @@ __host__ __device__ inline uint32_t sign_mask_fp6_packed(uint32_t h, int convent
 
 // Codebook entry e as packed int8 x 8 (= 4 * value), from either table format.  Sets *bad
 // when the entry cannot be decoded by XOR (byte not congruent to 2 mod 4, fp16 value not k/4).
-__device__ inline uint64_t load_entry(const void *cb, int cb_is_f16, int e, bool *bad) {
+__device__ inline uint64_t load_entry(const void *cb, int cb_is_f16, int e, bool *bad, const uint4 *pre = nullptr) {
     uint64_t v;
     if (!cb_is_f16) {
         v = static_cast<uint64_t>(reinterpret_cast<const int64_t *>(cb)[e]);
     } else {
-        const uint4 raw = reinterpret_cast<const uint4 *>(cb)[e];
+        const uint4 raw = pre != nullptr ? *pre : reinterpret_cast<const uint4 *>(cb)[e];
         const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
         v = 0;
         for (int i = 0; i < 8; ++i) {
@@ -274,8 +274,16 @@ __device__ inline uint64_t format_entry(uint64_t v, int fmt, bool *bad) {
 // Fills the table; every thread of the group calls it (tid in [0, nthreads)).
 // Returns true when this thread saw an entry that the XOR decode cannot represent.
 // packed_mask: store the kFmtFp6 masks as 32 replicas of the packed 32-bit word.
+// pre: the fp16 entry of thread tid (tid even, tid < 512), loaded earlier with lut_prefetch so that
+// the global-memory latency overlaps other set-up work (needs nthreads >= 512).
+__device__ __forceinline__ uint4 lut_prefetch(const void *cb16, int tid) {
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (tid < 512 && (tid & 1) == 0) v = __ldg(reinterpret_cast<const uint4 *>(cb16) + (tid >> 1));
+    return v;
+}
+
 __device__ inline bool lut_fill(uint32_t lut_addr, const void *cb, int cb_is_f16, int convention,
-                                int fmt, int tid, int nthreads, bool packed_mask = false) {
+                                int fmt, int tid, int nthreads, bool packed_mask = false, const uint4 *pre = nullptr) {
     bool bad = false;
     for (int i = tid; i < 512; i += nthreads) {
         const int e = i >> 1;
@@ -285,7 +293,7 @@ __device__ inline bool lut_fill(uint32_t lut_addr, const void *cb, int cb_is_f16
             const uint32_t w = sign_mask_fp6_packed(static_cast<uint32_t>(e), convention);
             rep = make_uint4(w, w, w, w);
         } else {
-            const uint64_t v = part == 0 ? format_entry(load_entry(cb, cb_is_f16, e, &bad), fmt, &bad)
+            const uint64_t v = part == 0 ? format_entry(load_entry(cb, cb_is_f16, e, &bad, pre), fmt, &bad)
                                          : sign_mask(static_cast<uint32_t>(e), convention, fmt);
             const uint32_t lo = static_cast<uint32_t>(v), hi = static_cast<uint32_t>(v >> 32);
             rep = make_uint4(lo, hi, lo, hi);

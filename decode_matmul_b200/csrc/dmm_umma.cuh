@@ -249,6 +249,7 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     if (tid == 0) DMM_STAMP(0, 0, 0);
+    const uint4 cb_pre = lut_prefetch(p.cb, tid);  // the codebook is static data: fetch it first
 
     if (ring_addr + Plan::kRingBytes > base + p.dyn_smem_bytes) {  // uniform over the grid
         if (tid == 0) raise_status(DMM_STATUS_BAD_SMEM);
@@ -292,7 +293,9 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
     }
     if (tid == 0) DMM_STAMP(0, 2, 1);
     if (warp == kUMmaWarp) tmem_alloc(smem_u32(const_cast<uint32_t *>(tmem_slot)), kUTmemCols);
-    for (uint32_t o = tid * 16u; o < Plan::kXBytes; o += kUThreads * 16u) sts128(x_addr + o, make_uint4(0, 0, 0, 0));
+    if constexpr (!Pol::kIsF8) {  // fp16 stages: rows past the batch must read as zero
+        for (uint32_t o = tid * 16u; o < Plan::kXBytes; o += kUThreads * 16u) sts128(x_addr + o, make_uint4(0, 0, 0, 0));
+    }
     fence_async_smem();
     tc_fence_before();
     if (tid == 0) DMM_STAMP(0, 2, 2);
@@ -349,17 +352,20 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
         }
         if (tid == 0) DMM_STAMP(0, 1, 0);
 
-        const bool bad = lut_fill(lut_addr, p.cb, 1, p.sign_convention, Pol::kFmt, tid, kUDecWarps * 32, Pol::kIsF8 != 0);
+        const bool bad = lut_fill(lut_addr, p.cb, 1, p.sign_convention, Pol::kFmt, tid, kUDecWarps * 32, Pol::kIsF8 != 0, &cb_pre);
         if (bad) raise_status(DMM_STATUS_BAD_CODEBOOK);
         if (tid == 0) DMM_STAMP(0, 1, 1);
         if (lane == 0) DMM_STAMP(0, 8 + warp, 0);
         named_barrier(1, kUDecWarps * 32);
-        while (iidx < RING && icur.ok) {  // ... the rest of the ring once the table is built
-            issue(icur, iidx);
-            icur.c += 4;
-            settle(icur);
-            ++iidx;
-        }
+        // ... the rest of the ring is filled after the first group has been handed over
+        auto top_up = [&](int chunks_done) {
+            while (iidx < chunks_done + RING && icur.ok) {
+                issue(icur, iidx);
+                icur.c += 4;
+                settle(icur);
+                ++iidx;
+            }
+        };
         const LutLane ll = lut_lane(lut_addr, lane, Pol::kIsF8 != 0);
         grid_dep_wait();
         if (tid == 0) DMM_STAMP(0, 0, 2);
@@ -433,15 +439,11 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
                     if (lane == 0) mbar_arrive(bar(Plan::kBarFull + sl));
                     if (tid == 0) DMM_STAMP(1, sA, 3);
                     ++sA;
+                    if (g0 + G < n) top_up(cidx);  // slots of finished chunks (and, at the start, the whole ring)
                 }
-                __syncwarp();  // every lane has read the slot: refill it
+                __syncwarp();  // every lane has read the slot: it may be refilled
                 if (tid == 0) DMM_STAMP(5, cidx, 2);
-                if (icur.ok) {
-                    issue(icur, iidx);
-                    icur.c += 4;
-                    settle(icur);
-                    ++iidx;
-                }
+                top_up(cidx + 1);
                 if (tid == 0) DMM_STAMP(5, cidx, 3);
                 ccur.c += 4;
                 settle(ccur);

@@ -234,3 +234,75 @@ def test_launches_are_counted(e8p):
     w = torch.zeros((16, 8), dtype=torch.int16, device="cuda")
     dmm.decode_matmul_i8(x, w, _dev(e8p))
     assert dmm.launch_count() == before + 1
+
+
+def test_atomic_accumulate_matches_oracle():
+    """DMM_FLAG_ATOMIC: partial sums are added with floating-point atomics; the result is the
+    product plus what the output held, up to summation order."""
+    rng = np.random.default_rng(31)
+    cb16 = o.synthetic_codebook(42)
+    for M, N, K in [(1, 8192, 8192), (3, 11008, 4096), (40, 2048, 4096)]:
+        x = rng.standard_normal((M, K)).astype(np.float16)
+        codes = _codes(rng, N, K)
+        base = rng.standard_normal((M, N)).astype(np.float32)
+        out = _dev(base)
+        y = dmm.decode_matmul_fp16(_dev(x), _dev(o.tile_pack(codes)), _dev(cb16), 1.0, out, accumulate=True, atomic=True)
+        _check_f16(y.cpu().numpy(), base + o.decode_matmul_f16(x, codes, cb16, 1.0))
+    with pytest.raises(RuntimeError):
+        dmm.decode_matmul_fp16(_dev(x), _dev(o.tile_pack(codes)), _dev(cb16), 1.0, out, atomic=True)
+
+
+def test_fused_inputs_and_zero_on_the_way():
+    """dmm_f16_fused: fp32 activations rounded by the loaders, silu(gate) * up formed by the
+    loaders, and a buffer cleared for a later accumulating call."""
+    rng = np.random.default_rng(32)
+    cb16 = o.synthetic_codebook(42)
+    for M, N, K in [(1, 4096, 8192), (3, 512, 1024), (8, 2048, 4096)]:
+        codes = _codes(rng, N, K)
+        tiled, cb = _dev(o.tile_pack(codes)), _dev(cb16)
+        gap = K + 64
+        a = rng.standard_normal((M, gap + K)).astype(np.float32)
+        later = torch.full((M, 1000), 7.0, dtype=torch.float32, device="cuda")
+        out = torch.zeros((M, N), dtype=torch.float32, device="cuda")
+        y = dmm.decode_matmul_fused(_dev(a), tiled, cb, 0.5, out, x_kind=dmm.X_F32, zero=later).cpu().numpy()
+        _check_f16(y, o.decode_matmul_f16(a[:, :K].astype(np.float16), codes, cb16, 0.5))
+        assert float(later.abs().max()) == 0.0
+        g, u = a[:, :K], a[:, gap:gap + K]
+        act = (g / (1.0 + np.exp(-g)) * u).astype(np.float16)
+        y2 = dmm.decode_matmul_fused(_dev(a), tiled, cb, 1.0, out, x_kind=dmm.X_F32_SILU_MUL, x_gap=gap).cpu().numpy()
+        want2 = o.decode_matmul_f16(act, codes, cb16, 1.0)
+        # __expf in the loaders vs numpy exp: an activation may round to the neighbouring half
+        assert np.linalg.norm(y2 - want2) / np.linalg.norm(want2) <= 2e-3
+        assert np.abs(y2 - want2).max() <= 0.25
+
+
+def test_linear_stack_fused_step_matches_unfused():
+    """The fused step of the stack (4 launches per block, no elementwise kernels) against the
+    plain step (separate cast / SiLU / residual kernels) and against the oracle for one block."""
+    from decode_matmul_b200.linear import LinearStack
+
+    cfg = dict(hidden=512, kv_heads=2, head_dim=64, ffn=1024, layers=3)
+    cb16 = dmm.synthetic_codebook(42)
+    stack = LinearStack(cfg, cb16, "cuda", seed=5, scale=2.0 ** -8)
+    torch.manual_seed(3)
+    h0 = torch.randn(2, 512, device="cuda")
+    h_fused = stack.step(h0.clone(), fused=True)
+    h_plain = stack.step(h0.clone(), fused=False)
+    assert torch.allclose(h_fused, h_plain, rtol=2e-3, atol=2e-3)
+    # first block on the CPU with the oracle
+    h = h0.cpu().numpy().astype(np.float32)
+    blk = stack.layers[0]
+    cbn = cb16.numpy()
+
+    def lin(name, x16):
+        codes = o.tile_unpack(blk[name].codes.cpu().numpy())
+        return o.decode_matmul_f16(x16, codes, cbn, blk[name].scale)
+
+    a = lin("qkv", h.astype(np.float16))
+    h = h + lin("o", a[:, :512].astype(np.float16))
+    g = lin("gate_up", h.astype(np.float16))
+    act = (g[:, :1024] / (1 + np.exp(-g[:, :1024])) * g[:, 1024:]).astype(np.float16)
+    h = h + lin("down", act)
+    one = LinearStack(dict(cfg, layers=1), cb16, "cuda", seed=5, scale=2.0 ** -8)
+    got = one.step(h0.clone(), fused=True).cpu().numpy()
+    assert np.abs(got - h).max() <= 2e-3

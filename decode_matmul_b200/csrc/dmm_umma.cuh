@@ -24,16 +24,17 @@
 // numbered super-tile-major and split evenly and contiguously over the CTAs (stream-K); the
 // part of a super-tile a CTA owns is a segment.
 //
-// Warp roles (22 warps):
+// Warp roles (23 warps):
 //   0..15  decoders, four groups of four warps.  Group q takes chunks q, q+4, ... (C tiles
 //          each) of a segment.  Warp wq of a group owns TMEM lanes 32wq..32wq+31 = strips
 //          4wq..4wq+3; it streams its own strips through a private TMA ring, decodes, writes
 //          A stage buffers in TMEM and signals its MMA issuer.  Groups 0 and 1 also run the
 //          epilogue of tile 0 and tile 1.
-//   16..19 MMA issuers (one thread each); issuer s serves the decoder groups q with
+//   16..19 MMA issuers (one elected thread each); issuer s serves the decoder groups q with
 //          q % kNAcc == s and owns accumulator s of both MMA tiles.  Warp 16 also allocates
 //          the tensor memory.
 //   20..21 activation loaders.
+//   22     TMA producer (one thread): streams the code chunks into the groups' rings.
 // Every wait is bounded (mbar_wait); nothing spins on another CTA.
 #pragma once
 #include <cuda.h>
@@ -136,9 +137,9 @@ struct PolF8 {
     static constexpr int kIsF8 = 1;
     static constexpr int kFmt = kFmtFp6;
     static constexpr int kG = 2;
-    static constexpr int kNA = 3;
+    static constexpr int kNA = 2;
     static constexpr int kC = 4;
-    static constexpr int kRing = 3;    // chunks in flight per decoder warp
+    static constexpr int kRing = 3;    // chunks in flight per decoder group
     static constexpr int kACols = 8;   // TMEM columns of one k-tile of one MMA tile (32 k x 1 byte)
     static constexpr uint32_t x_tile_bytes(int) { return 1024; }  // 2 k-halves x (4 planes x 8 rows) x 16 B
     static constexpr int out_cols(int) { return 8; }                // batch columns per launch
@@ -155,14 +156,14 @@ struct PolF16 {
     static constexpr int out_cols(int nmma) { return nmma; }
 };
 
-constexpr int kUDecWarps = 16, kUMmaWarp = 16, kUMmaWarps = 2, kULoadWarps = 2;
-constexpr int kUThreads = (kUDecWarps + kUMmaWarps + kULoadWarps) * 32;
+constexpr int kUDecWarps = 16, kUMmaWarp = 16, kUMmaWarps = 4, kULoadWarps = 2, kUTmaWarp = 22;
+constexpr int kUThreads = (kUDecWarps + kUMmaWarps + kULoadWarps + 1) * 32;
 constexpr uint32_t kUBarBytes = 2048;
 constexpr uint32_t kUTmemCols = 512;
 
 template <class Pol, int NMMA>
 struct UmmaPlan {
-    static constexpr int kNAcc = 2;                               // accumulators per MMA tile = issuers
+    static constexpr int kNAcc = Pol::kIsF8 ? 4 : 2;              // accumulators per MMA tile = active issuers
     static constexpr uint32_t kDCols = 2 * kNAcc * NMMA;          // TMEM: accumulators first
     static constexpr uint32_t kBufCols = 2 * Pol::kG * Pol::kACols;  // one group buffer: [tile][k-tile][cols]
     static constexpr uint32_t kACols = 4 * Pol::kNA * kBufCols;
@@ -176,16 +177,17 @@ struct UmmaPlan {
     static constexpr uint32_t kXBytes = Pol::kIsF8 ? kEpochs * kEpochBytes + 256 : kSlots * kXStage;
     static constexpr int kNB = Pol::out_cols(NMMA);               // output columns per launch
     static constexpr uint32_t kPreBytes = kUBarBytes + kXBytes;
-    static constexpr uint32_t kSlotBytes = 4 * Pol::kC * 128;     // ring slot: 4 strips x C k-tiles
-    static constexpr uint32_t kRingBytes = kUDecWarps * Pol::kRing * kSlotBytes;
+    static constexpr uint32_t kSlotBytes = 16 * Pol::kC * 128;    // ring slot: 16 strips x C k-tiles (one TMA box)
+    static constexpr uint32_t kRingBytes = 4 * Pol::kRing * kSlotBytes;  // one ring per decoder group
     static constexpr uint32_t kDynBytes = 0x10000u - 0x400u + kLutBytes + kRingBytes;
     static constexpr int kPartial = 2 * kNB * 128;                // output values per segment
     static_assert(kPreBytes <= 0x10000u - 0x400u, "activation stages do not fit below the table");
     static_assert(kDynBytes <= 232448u, "shared memory plan exceeds the per-CTA limit");
     static_assert(Pol::kC % Pol::kG == 0, "a chunk must hold whole groups");
     // barrier indices
-    static constexpr int kBarCode = 0;                                   // [16][kRing]  TMA completion
-    static constexpr int kBarFull = kBarCode + kUDecWarps * Pol::kRing;  // [kSlots] 4 decoder warps + 1 loader
+    static constexpr int kBarCode = 0;                                   // [4][kRing] TMA completion
+    static constexpr int kBarEmpty = kBarCode + 4 * Pol::kRing;          // [4][kRing] the group's 4 warps are done
+    static constexpr int kBarFull = kBarEmpty + 4 * Pol::kRing;          // [kSlots] decoder warps (+ fp16 loader)
     static constexpr int kBarFree = kBarFull + kSlots;                   // [kSlots] tcgen05.commit
     static constexpr int kBarXReady = kBarFree + kSlots;                 // [kEpochs] loader warps
     static constexpr int kBarXFree = kBarXReady + kEpochs;               // [kEpochs] both issuers (commit)
@@ -231,7 +233,7 @@ struct UmmaParams {
 #endif
 
 // `codes_map` is a 2-D tensor map of the tiled code matrix: inner dimension = one strip
-// (K/32 k-tiles x 32 uint32), outer dimension = strips; box = kC k-tiles x 4 strips.
+// (K/32 k-tiles x 32 uint32), outer dimension = strips; box = kC k-tiles x 16 strips.
 template <class Pol, int NMMA>
 __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
                                                             const __grid_constant__ CUtensorMap codes_map) {
@@ -279,6 +281,7 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
     // ---- set-up: barriers, TMEM, zeroed activation stages ----
     if (tid < Plan::kBarCount) {
         uint32_t count = 1;                                                  // TMA, tcgen05.commit
+        if (tid >= Plan::kBarEmpty && tid < Plan::kBarFull) count = 4;
         if (tid >= Plan::kBarFull && tid < Plan::kBarFree) count = Pol::kIsF8 ? 4 : 5;  // decoder warps (+ loader)
         if (tid >= Plan::kBarXReady && tid < Plan::kBarXFree) count = kULoadWarps;
         if (tid >= Plan::kBarXFree && tid < Plan::kBarDReady) count = NACC;
@@ -308,48 +311,7 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
     if (warp < kUDecWarps) {
         // =============================== decoders ===============================
         const int q = warp >> 2, wq = warp & 3;
-        const uint32_t wring = ring_addr + static_cast<uint32_t>(warp) * (RING * Plan::kSlotBytes);
-        const uint64_t policy = policy_evict_first();
-
-        struct Cur {
-            int ss, c, cbase;  // segment, chunk inside it, chunks of earlier segments
-            bool ok;
-        };
-        auto settle = [&](Cur &cu) {  // first chunk of group q at or after (ss, c)
-            while (cu.ok && cu.c * C >= seg_len(cu.ss)) {
-                if (cu.ss == ss_last) {
-                    cu.ok = false;
-                } else {
-                    cu.cbase += seg_chunks(cu.ss);
-                    ++cu.ss;
-                    cu.c = (q - cu.cbase) & 3;
-                }
-            }
-        };
-        // one tiled TMA load per chunk: kC k-tiles x this warp's 4 strips (always the full box:
-        // k-tiles past the segment are simply not used, strips past N read as zero)
-        auto issue = [&](const Cur &cu, int idx) {
-            if (lane == 0) {
-                const int kt = seg_kt0(cu.ss) + cu.c * C;
-                const uint32_t b = bar(Plan::kBarCode + warp * RING + idx % RING);
-                mbar_arrive_expect_tx(b, Plan::kSlotBytes);
-                tma_load_2d(wring + (idx % RING) * Plan::kSlotBytes, &codes_map, kt * 32, cu.ss * 16 + wq * 4, b, policy);
-            }
-        };
-
-        if (tid == 0) DMM_STAMP(0, 3, 0);
-        Cur icur{ss_first, q, 0, true}, ccur;
-        settle(icur);
-        ccur = icur;
-        int iidx = 0, cidx = 0;
-        if (tid == 0) DMM_STAMP(0, 3, 1);
-        if (icur.ok) {  // first chunk now (weights do not depend on the previous kernel) ...
-            issue(icur, iidx);
-            if (tid == 0) DMM_STAMP(0, 3, 2);
-            icur.c += 4;
-            settle(icur);
-            ++iidx;
-        }
+        const uint32_t gring = ring_addr + static_cast<uint32_t>(q) * (RING * Plan::kSlotBytes);  // ring of group q
         if (tid == 0) DMM_STAMP(0, 1, 0);
 
         const bool bad = lut_fill(lut_addr, p.cb, 1, p.sign_convention, Pol::kFmt, tid, kUDecWarps * 32, Pol::kIsF8 != 0, &cb_pre);
@@ -357,15 +319,6 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
         if (tid == 0) DMM_STAMP(0, 1, 1);
         if (lane == 0) DMM_STAMP(0, 8 + warp, 0);
         named_barrier(1, kUDecWarps * 32);
-        // ... the rest of the ring is filled after the first group has been handed over
-        auto top_up = [&](int chunks_done) {
-            while (iidx < chunks_done + RING && icur.ok) {
-                issue(icur, iidx);
-                icur.c += 4;
-                settle(icur);
-                ++iidx;
-            }
-        };
         const LutLane ll = lut_lane(lut_addr, lane, Pol::kIsF8 != 0);
         grid_dep_wait();
         if (tid == 0) DMM_STAMP(0, 0, 2);
@@ -378,15 +331,18 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
         const uint32_t tlane = tmem + (static_cast<uint32_t>(wq * 32) << 16);
         uint32_t sA = 0;  // groups this decoder group has produced
         int segidx = 0, ebase = 0;
+        int cidx = 0;  // chunks this group has consumed
         for (int ss = ss_first; ss <= ss_last; ebase += seg_chunks(ss), ++ss, ++segidx) {
-            while (ccur.ok && ccur.ss == ss) {
-                const int len = seg_len(ss);
-                const int n = len - ccur.c * C < C ? len - ccur.c * C : C;  // k-tiles in this chunk
+            const int len = seg_len(ss);
+            const int nchunks_ss = (len + C - 1) / C;
+            for (int c = (q - ebase) & 3; c < nchunks_ss; c += 4) {
+                const int n = len - c * C < C ? len - c * C : C;  // k-tiles in this chunk
                 const int slot = cidx % RING;
                 if (tid == 0) DMM_STAMP(5, cidx, 0);
-                mbar_wait(bar(Plan::kBarCode + warp * RING + slot), static_cast<uint32_t>((cidx / RING) & 1), flags);
+                mbar_wait(bar(Plan::kBarCode + q * RING + slot), static_cast<uint32_t>((cidx / RING) & 1), flags);
                 if (tid == 0) DMM_STAMP(5, cidx, 1);
-                const uint32_t src = wring + slot * Plan::kSlotBytes + (lane >> 3) * (C * 128) + (lane & 7) * 16;
+                // slot layout [16 strips][C k-tiles][128 B]; this lane: strip 4*wq + lane/8, piece lane%8
+                const uint32_t src = gring + slot * Plan::kSlotBytes + (wq * 4 + (lane >> 3)) * (C * 128) + (lane & 7) * 16;
 #pragma unroll 1
                 for (int g0 = 0; g0 < n; g0 += G) {
                     const int buf = static_cast<int>(sA % NA);
@@ -439,23 +395,19 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
                     if (lane == 0) mbar_arrive(bar(Plan::kBarFull + sl));
                     if (tid == 0) DMM_STAMP(1, sA, 3);
                     ++sA;
-                    if (g0 + G < n) top_up(cidx);  // slots of finished chunks (and, at the start, the whole ring)
                 }
-                __syncwarp();  // every lane has read the slot: it may be refilled
+                __syncwarp();  // every lane has read the slot: hand it back to the TMA warp
+                if (lane == 0) mbar_arrive(bar(Plan::kBarEmpty + q * RING + slot));
                 if (tid == 0) DMM_STAMP(5, cidx, 2);
-                top_up(cidx + 1);
-                if (tid == 0) DMM_STAMP(5, cidx, 3);
-                ccur.c += 4;
-                settle(ccur);
                 ++cidx;
             }
 
             if (q < 2) {
                 // ---------------- epilogue of MMA tile q of this segment ----------------
-                const int len = seg_len(ss);
-                const int nchunks = (len + C - 1) / C;
+                const int nchunks = nchunks_ss;
                 // accumulator a was written in this segment iff one of its chunks has parity a
-                const uint32_t used = nchunks >= 2 ? 3u : (1u << (ebase & 1));
+                uint32_t used = 0;
+                for (int cc = 0; cc < nchunks && cc < NACC; ++cc) used |= 1u << ((ebase + cc) % NACC);
                 if (tid == 0) DMM_STAMP(4, segidx, 0);
                 mbar_wait(bar(Plan::kBarDReady), static_cast<uint32_t>(segidx & 1), flags);
                 tc_fence_after();
@@ -554,22 +506,13 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
                 if (tid == 0) DMM_STAMP(4, segidx, 2);
             }
         }
-        if (flags[0]) {
-            // A wait gave up: bulk copies of this warp may still be in flight.  Give each ring
-            // slot a last bounded chance to land before the CTA releases its shared memory.
-            for (int d = 0; d < RING && d < iidx; ++d) {
-                const int idx = iidx - 1 - d;
-                mbar_wait_limit(bar(Plan::kBarCode + warp * RING + idx % RING), static_cast<uint32_t>((idx / RING) & 1),
-                                20ll * 1000 * 1000);
-            }
-        }
     } else if (warp < kUMmaWarp + kUMmaWarps) {
         // =============================== MMA issuers ===============================
-        // issuer `me` serves decoder groups q with (q & 1) == me and owns accumulator `me`
+        // issuer `me` serves the decoder groups q with q % kNAcc == me and owns accumulator `me`
         // The whole warp runs the loop converged (so that addresses and descriptors stay in
         // uniform registers); one elected lane issues the tcgen05 instructions.
         const int me = warp - kUMmaWarp;
-        {
+        if (me < NACC) {
             const bool leader = elect_one();
             uint32_t cnt0 = 0, cnt1 = 0;  // groups consumed from decoder groups me and me + 2
             int segidx = 0;
@@ -600,17 +543,17 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
                     tc_fence_after();
                 }
                 bool first = true;  // the accumulators hold nothing of this segment yet
-                for (int c = (me - cbase) & 1; c < nchunks; c += 2) {
+                for (int c = (me - cbase) & (NACC - 1); c < nchunks; c += NACC) {
                     const int q = (cbase + c) & 3;
                     const int n = len - c * C < C ? len - c * C : C;
 #pragma unroll 1
                     for (int g0 = 0; g0 < n; g0 += G) {
                         const uint32_t cn = q < 2 ? cnt0 : cnt1;
                         const int sl = q * NA + static_cast<int>(cn % NA);
-                        if (me == 0 && leader) DMM_STAMP(2, cn, 0);
+                        if (me == 0 && leader) DMM_STAMP(2, cn * 2 + (q >> 1), 0);
                         mbar_wait(bar(Plan::kBarFull + sl), (cn / NA) & 1, flags);
                         tc_fence_after();
-                        if (me == 0 && leader) DMM_STAMP(2, cn, 1);
+                        if (me == 0 && leader) DMM_STAMP(2, cn * 2 + (q >> 1), 1);
                         const uint64_t xd = xdesc0 + ((static_cast<uint32_t>(sl) * Plan::kXStage) >> 4);
                         const uint32_t a_col = tmem + Plan::kDCols + static_cast<uint32_t>(sl) * Plan::kBufCols;
                         if constexpr (Pol::kIsF8) {
@@ -643,7 +586,7 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
                         }
                         first = false;
                         if (leader) tc_commit(bar(Plan::kBarFree + sl));
-                        if (me == 0 && leader) DMM_STAMP(2, cn, 2);
+                        if (me == 0 && leader) DMM_STAMP(2, cn * 2 + (q >> 1), 2);
                         if (q < 2) ++cnt0; else ++cnt1;
                     }
                 }
@@ -655,11 +598,45 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
                     if (leader) tc_commit(bar(Plan::kBarXFree + r % Plan::kEpochs));
             }
         }
+    } else if (warp == kUTmaWarp) {
+        // =============================== TMA producer ===============================
+        // One thread streams the codes: chunk after chunk in the CTA-wide chunk order, each chunk
+        // one tiled load (16 strips x C k-tiles) into the ring of the decoder group it belongs to.
+        // Always the full box: k-tiles past the segment are not used, strips past N read as zero.
+        if (lane == 0) {
+            const uint64_t policy = policy_evict_first();
+            uint32_t cnt[4] = {0, 0, 0, 0};  // chunks issued per decoder group
+            int cbase = 0;
+            for (int ss = ss_first; ss <= ss_last; cbase += seg_chunks(ss), ++ss) {
+                const int nchunks = seg_chunks(ss), kt0 = seg_kt0(ss);
+                for (int c = 0; c < nchunks; ++c) {
+                    const int q = (cbase + c) & 3;
+                    const uint32_t n_q = q == 0 ? cnt[0] : q == 1 ? cnt[1] : q == 2 ? cnt[2] : cnt[3];
+                    const int slot = static_cast<int>(n_q % RING);
+                    if (n_q >= RING)
+                        mbar_wait(bar(Plan::kBarEmpty + q * RING + slot), ((n_q / RING) - 1) & 1, flags);
+                    const uint32_t b = bar(Plan::kBarCode + q * RING + slot);
+                    mbar_arrive_expect_tx(b, Plan::kSlotBytes);
+                    tma_load_2d(ring_addr + (q * RING + slot) * Plan::kSlotBytes, &codes_map, (kt0 + c * C) * 32, ss * 16, b, policy);
+                    if (q == 0) ++cnt[0]; else if (q == 1) ++cnt[1]; else if (q == 2) ++cnt[2]; else ++cnt[3];
+                }
+            }
+            if (flags[0]) {
+                // A wait gave up somewhere: loads may still be in flight.  Give the last load of
+                // every ring slot a bounded chance to land before the CTA releases its shared memory.
+                for (int q = 0; q < 4; ++q)
+                    for (uint32_t d = 0; d < RING && d < cnt[q]; ++d) {
+                        const uint32_t idx = cnt[q] - 1 - d;
+                        mbar_wait_limit(bar(Plan::kBarCode + q * RING + static_cast<int>(idx % RING)), (idx / RING) & 1,
+                                        20ll * 1000 * 1000);
+                    }
+            }
+        }
     } else {
         // =========================== activation loaders ===========================
         // loader wl serves the chunks of parity wl (the chunks of issuer wl), one chunk per pass
         grid_dep_wait();
-        const int wl = warp - kUMmaWarp - kUMmaWarps;
+        const int wl = warp - kUMmaWarp - kUMmaWarps;  // warps 20, 21
         const __half *x = reinterpret_cast<const __half *>(p.x);
         const int M = static_cast<int>(p.M);
         const int ppt = M * 4;  // 16-byte pieces per k-tile: (row, 8-k chunk)
@@ -812,13 +789,13 @@ inline EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
-// Tensor map of the tiled code matrix seen as uint32 [strips][K/32 * 32], box = c_tiles k-tiles x 4 strips.
+// Tensor map of the tiled code matrix seen as uint32 [strips][K/32 * 32], box = c_tiles k-tiles x 16 strips.
 inline int make_codes_map(CUtensorMap *map, const void *codes, long long N, long long K, int c_tiles) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (fn == nullptr) return cudaErrorNotSupported;
     const cuuint64_t gdim[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(N / 16)};  // K/32 tiles x 32 words
     const cuuint64_t gstride[1] = {static_cast<cuuint64_t>(K) * 4};                               // bytes per strip
-    const cuuint32_t box[2] = {static_cast<cuuint32_t>(c_tiles * 32), 4};
+    const cuuint32_t box[2] = {static_cast<cuuint32_t>(c_tiles * 32), 16};
     const cuuint32_t estride[2] = {1, 1};
     const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void *>(codes), gdim, gstride, box, estride,
                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,

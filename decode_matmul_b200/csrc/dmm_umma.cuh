@@ -329,6 +329,10 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
         }
 
         const uint32_t tlane = tmem + (static_cast<uint32_t>(wq * 32) << 16);
+        // The four groups share the shared-memory look-up pipe and are otherwise independent:
+        // start them a fraction of a group apart so that one group's hand-over and waiting
+        // falls into the others' look-up bursts instead of all groups idling together.
+        if (q != 0) __nanosleep(static_cast<unsigned>(q) * 128u);
         uint32_t sA = 0;  // groups this decoder group has produced
         int segidx = 0, ebase = 0;
         int cidx = 0;  // chunks this group has consumed

@@ -156,8 +156,24 @@ struct PolF16 {
     static constexpr int out_cols(int nmma) { return nmma; }
 };
 
-constexpr int kUDecWarps = 16, kUMmaWarp = 16, kUMmaWarps = 4, kULoadWarps = 2, kUTmaWarp = 22;
+constexpr int kUDecWarps = 16, kUMmaWarp = 16, kUMmaWarps = 4, kULoadWarps = 4, kULoadTeams = 2, kUTmaWarp = 24;
 constexpr int kUThreads = (kUDecWarps + kUMmaWarps + kULoadWarps + 1) * 32;
+constexpr int kFirstEpoch = 16;  // k-tiles in the first activation epoch of a CTA at batch 1 (fp8 policy)
+constexpr int kMaxEpoch = 48;    // and at most this many in the later ones: short epochs keep the
+                                 // loaders' latency per epoch below the time the previous one lasts
+
+// k-tiles of the first epoch: one 16-byte piece per thread of a loader team (4 * M pieces per tile)
+__host__ __device__ inline int first_epoch_tiles(int E, int M) {
+    int e0 = (kFirstEpoch / M) & ~1;
+    if (e0 < 2) e0 = 2;
+    return e0 < E ? e0 : E;
+}
+
+// k-tiles per activation epoch: what fits in one epoch buffer, even, at most kMaxEpoch
+__host__ __device__ inline int epoch_tiles(uint32_t epoch_bytes, uint32_t tile_bytes) {
+    const int fit = static_cast<int>((epoch_bytes / tile_bytes) & ~1u);
+    return fit < kMaxEpoch ? fit : kMaxEpoch;
+}
 constexpr uint32_t kUBarBytes = 2048;
 constexpr uint32_t kUTmemCols = 512;
 
@@ -283,7 +299,7 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
         uint32_t count = 1;                                                  // TMA, tcgen05.commit
         if (tid >= Plan::kBarEmpty && tid < Plan::kBarFull) count = 4;
         if (tid >= Plan::kBarFull && tid < Plan::kBarFree) count = Pol::kIsF8 ? 4 : 5;  // decoder warps (+ loader)
-        if (tid >= Plan::kBarXReady && tid < Plan::kBarXFree) count = kULoadWarps;
+        if (tid >= Plan::kBarXReady && tid < Plan::kBarXFree) count = kULoadWarps / kULoadTeams;
         if (tid >= Plan::kBarXFree && tid < Plan::kBarDReady) count = NACC;
         if (tid == Plan::kBarDReady) count = NACC;
         if (tid == Plan::kBarDFree) count = 8;
@@ -525,9 +541,10 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
                                        : ((1u << 4) | ((NMMA >> 3) << 17) | ((128u >> 4) << 24));
             // descriptor of activation stage 0; later stages and k-halves only move the address field
             const uint32_t tile_b = 128u * static_cast<uint32_t>(p.M);  // fp8: bytes of one k-tile of planes
-            const int E = static_cast<int>((Plan::kEpochBytes / tile_b) & ~1u);  // k-tiles per epoch
+            const int E = epoch_tiles(Plan::kEpochBytes, tile_b);  // k-tiles per epoch
+            const int E0 = first_epoch_tiles(E, static_cast<int>(p.M));           // the first one is short
             const uint64_t xdesc0 = Pol::kIsF8 ? smem_desc(x_addr, tile_b / 2, tile_b / 8) : smem_desc(x_addr, NMMA * 16, 128);
-            int cur_ep = -1, ep_end = 0;  // fp8: epoch whose buffer is being read; first tile past it
+            int cur_ep = -1, ep_beg = 0, ep_end = 0;  // fp8: epoch being read and its k-tile range
             uint32_t ep_addr = 0;
             auto enter_epoch = [&](int e) {
                 // every earlier epoch is finished for this issuer: let the loaders reuse its buffer
@@ -535,7 +552,8 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
                     if (leader) tc_commit(bar(Plan::kBarXFree + r % Plan::kEpochs));
                 mbar_wait(bar(Plan::kBarXReady + e % Plan::kEpochs), static_cast<uint32_t>((e / Plan::kEpochs) & 1), flags);
                 cur_ep = e;
-                ep_end = (e + 1) * E;
+                ep_beg = e == 0 ? 0 : E0 + (e - 1) * E;
+                ep_end = E0 + e * E;
                 ep_addr = ((e % Plan::kEpochs) * Plan::kEpochBytes) >> 4;
             };
             int cbase = 0, jseg = 0;  // chunks / k-tiles of earlier segments
@@ -567,8 +585,8 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
                             for (int i = 0; i < G; ++i) {
                                 if (g0 + i < n) {
                                     const int jt = jseg + c * C + g0 + i;  // CTA-wide k-tile index
-                                    if (jt >= ep_end) enter_epoch(jt / E);
-                                    const uint64_t xt = xdesc0 + ep_addr + ((static_cast<uint32_t>(jt - (ep_end - E)) * tile_b) >> 4);
+                                    if (jt >= ep_end) enter_epoch(jt < E0 ? 0 : 1 + (jt - E0) / E);
+                                    const uint64_t xt = xdesc0 + ep_addr + ((static_cast<uint32_t>(jt - ep_beg) * tile_b) >> 4);
                                     const uint32_t acc = (first && i == 0) ? 0u : 1u;
                                     if (leader) {
 #pragma unroll
@@ -597,7 +615,7 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
                 if (leader) tc_commit(bar(Plan::kBarDReady));
             }
             if constexpr (Pol::kIsF8) {
-                const int nep = (i1 - i0 + E - 1) / E;
+                const int nep = i1 - i0 <= E0 ? 1 : 1 + (i1 - i0 - E0 + E - 1) / E;
                 for (int r = cur_ep < 0 ? 0 : cur_ep; r < nep; ++r)
                     if (leader) tc_commit(bar(Plan::kBarXFree + r % Plan::kEpochs));
             }
@@ -640,7 +658,7 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
         // =========================== activation loaders ===========================
         // loader wl serves the chunks of parity wl (the chunks of issuer wl), one chunk per pass
         grid_dep_wait();
-        const int wl = warp - kUMmaWarp - kUMmaWarps;  // warps 20, 21
+        const int wl = warp - kUMmaWarp - kUMmaWarps;  // warps 20 .. 23
         const __half *x = reinterpret_cast<const __half *>(p.x);
         const int M = static_cast<int>(p.M);
         const int ppt = M * 4;  // 16-byte pieces per k-tile: (row, 8-k chunk)
@@ -654,18 +672,24 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
             // descriptors straight into these buffers.  A piece is 8 consecutive k of one row.
             constexpr int U = 4;  // pieces in flight per thread
             const uint32_t tile_b = 128u * static_cast<uint32_t>(M);
-            const int E = static_cast<int>((Plan::kEpochBytes / tile_b) & ~1u);
+            const int E = epoch_tiles(Plan::kEpochBytes, tile_b);
+            // The first epoch is short: nothing can be multiplied before it is staged, and the
+            // loaders may only start once the previous kernel of the stream has finished.
+            const int E0 = first_epoch_tiles(E, M);
             const int ntiles = i1 - i0;
-            const int nep = (ntiles + E - 1) / E;
-            const int lt = wl * 32 + lane;
-            constexpr int LT = kULoadWarps * 32;
+            const int nep = ntiles <= E0 ? 1 : 1 + (ntiles - E0 + E - 1) / E;
+            // two teams of loader warps fill alternate epochs, so that the global-memory latency
+            // of one epoch overlaps the plane split of the other
+            const int lt = (wl / kULoadTeams) * 32 + lane;
+            constexpr int LT = kULoadWarps / kULoadTeams * 32;
             const float *xf = reinterpret_cast<const float *>(p.x);
-            for (int e = 0; e < nep; ++e) {
+            for (int e = wl % kULoadTeams; e < nep; e += kULoadTeams) {
                 if (wl == 0 && lane == 0) DMM_STAMP(3, e, 0);
                 if (e >= Plan::kEpochs)
                     mbar_wait(bar(Plan::kBarXFree + e % Plan::kEpochs), static_cast<uint32_t>(((e / Plan::kEpochs) - 1) & 1), flags);
-                const int t_lo = e * E;
-                const int nt = ntiles - t_lo < E ? ntiles - t_lo : E;
+                const int t_lo = e == 0 ? 0 : E0 + (e - 1) * E;
+                const int e_len = e == 0 ? E0 : E;
+                const int nt = ntiles - t_lo < e_len ? ntiles - t_lo : e_len;
                 const int npieces = nt * ppt;
                 const uint32_t ebuf = x_addr + (e % Plan::kEpochs) * Plan::kEpochBytes;
                 for (int pbase = 0; pbase < npieces; pbase += LT * U) {
@@ -693,7 +717,7 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
                                     const float4 b1 = __ldcg(reinterpret_cast<const float4 *>(xf + row * p.x_ld + p.x_gap + k0 + 4));
                                     const float g[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
 #pragma unroll
-                                    for (int j = 0; j < 8; ++j) f[j] = f[j] / (1.0f + __expf(-f[j])) * g[j];
+                                    for (int j = 0; j < 8; ++j) f[j] = __fdividef(f[j], 1.0f + __expf(-f[j])) * g[j];
                                 }
 #pragma unroll
                                 for (int j = 0; j < 4; ++j) {
@@ -737,7 +761,8 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
                 pend_q[0] = pend_q[1]; pend_cn[0] = pend_cn[1]; pend_ng[0] = pend_ng[1];
                 --npend;
             };
-            for (int ss = ss_first; ss <= ss_last; cbase += seg_chunks(ss), ++ss) {
+            // (two loader warps do this; the other two only work under the fp8 policy)
+            for (int ss = ss_first; wl < 2 && ss <= ss_last; cbase += seg_chunks(ss), ++ss) {
                 const int len = seg_len(ss), nchunks = seg_chunks(ss), kt0 = seg_kt0(ss);
                 for (int c = (wl - cbase) & 1; c < nchunks; c += 2) {
                     const int q = (cbase + c) & 3;

@@ -120,6 +120,11 @@ __device__ __forceinline__ uint64_t policy_evict_first() {
     return p;
 }
 
+// arrives at a named barrier without waiting for it
+__device__ __forceinline__ void named_barrier_arrive(int id, int threads) {
+    __threadfence_block();
+    asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
 __device__ __forceinline__ void named_barrier(int id, int threads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
@@ -274,11 +279,13 @@ __device__ inline uint64_t format_entry(uint64_t v, int fmt, bool *bad) {
 // Fills the table; every thread of the group calls it (tid in [0, nthreads)).
 // Returns true when this thread saw an entry that the XOR decode cannot represent.
 // packed_mask: store the kFmtFp6 masks as 32 replicas of the packed 32-bit word.
-// pre: the fp16 entry of thread tid (tid even, tid < 512), loaded earlier with lut_prefetch so that
+// Work item i < 512: entry row i & 255, half i >> 8 (0 = table entry, 1 = sign mask), so that the
+// lanes of a warp all take the same branch.
+// pre: the fp16 entry of thread tid (tid < 256), loaded earlier with lut_prefetch so that
 // the global-memory latency overlaps other set-up work (needs nthreads >= 512).
 __device__ __forceinline__ uint4 lut_prefetch(const void *cb16, int tid) {
     uint4 v = make_uint4(0, 0, 0, 0);
-    if (tid < 512 && (tid & 1) == 0) v = __ldg(reinterpret_cast<const uint4 *>(cb16) + (tid >> 1));
+    if (tid < 256) v = __ldg(reinterpret_cast<const uint4 *>(cb16) + tid);
     return v;
 }
 
@@ -286,8 +293,8 @@ __device__ inline bool lut_fill(uint32_t lut_addr, const void *cb, int cb_is_f16
                                 int fmt, int tid, int nthreads, bool packed_mask = false, const uint4 *pre = nullptr) {
     bool bad = false;
     for (int i = tid; i < 512; i += nthreads) {
-        const int e = i >> 1;
-        const int part = i & 1;
+        const int e = i & 255;
+        const int part = i >> 8;
         uint4 rep;
         if (part == 1 && packed_mask) {
             const uint32_t w = sign_mask_fp6_packed(static_cast<uint32_t>(e), convention);

@@ -89,6 +89,19 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
         : "r"(taddr)
         : "memory");
 }
+__device__ __forceinline__ uint32_t tmem_ld1(uint32_t taddr) {
+    uint32_t r;
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=r"(r) : "r"(taddr) : "memory");
+    return r;
+}
+// wait::ld that also names the loaded registers, so that no use of them can be moved above it
+__device__ __forceinline__ void tmem_wait_ld(uint32_t (&r)[16]) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]), "+r"(r[8]),
+                   "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15])
+                 :
+                 : "memory");
+}
 // D[tmem] (+)= A[tmem] * B[smem descriptor]
 __device__ __forceinline__ void mma_ts_f16(uint32_t d, uint32_t a, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
     asm volatile(
@@ -294,31 +307,51 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
     // go to different groups, also across a segment boundary.
 
     if (tid == 0) DMM_STAMP(0, 2, 0);
-    // ---- set-up: barriers, TMEM, zeroed activation stages ----
-    if (tid < Plan::kBarCount) {
-        uint32_t count = 1;                                                  // TMA, tcgen05.commit
-        if (tid >= Plan::kBarEmpty && tid < Plan::kBarFull) count = 4;
-        if (tid >= Plan::kBarFull && tid < Plan::kBarFree) count = Pol::kIsF8 ? 4 : 5;  // decoder warps (+ loader)
-        if (tid >= Plan::kBarXReady && tid < Plan::kBarXFree) count = kULoadWarps / kULoadTeams;
-        if (tid >= Plan::kBarXFree && tid < Plan::kBarDReady) count = NACC;
-        if (tid == Plan::kBarDReady) count = NACC;
-        if (tid == Plan::kBarDFree) count = 8;
-        mbar_init(bar(tid), count);
-        if (tid == 0) {
-            flags[0] = 0;
-            flags[1] = 0;
+    // ---- set-up ----
+    // The decoder warps build the look-up table straight away; the other warps initialise the
+    // barriers, allocate TMEM and zero the fp16 activation stages meanwhile and then go on
+    // (the code stream starts flowing while the table is still being built).  The decoders
+    // join through barrier 4, on which the others only arrive.
+    constexpr int kOtherThreads = kUThreads - kUDecWarps * 32;
+    bool bad_cb = false;
+    if (warp < kUDecWarps) {
+        if (tid == 0) DMM_STAMP(0, 1, 0);
+        bad_cb = lut_fill(lut_addr, p.cb, 1, p.sign_convention, Pol::kFmt, tid, kUDecWarps * 32, Pol::kIsF8 != 0, &cb_pre);
+        if (tid == 0) DMM_STAMP(0, 1, 1);
+        if (lane == 0) DMM_STAMP(0, 8 + warp, 0);
+        named_barrier(4, kUThreads);
+    } else {
+        const int ot = tid - kUDecWarps * 32;  // 0 .. kOtherThreads-1
+        const int bt = ot - kUMmaWarps * 32;   // loader and TMA warps initialise the barriers
+        if (bt == 0) DMM_STAMP(0, 3, 0);
+        if (bt >= 0 && bt < Plan::kBarCount) {
+            uint32_t count = 1;                                                // TMA, tcgen05.commit
+            if (bt >= Plan::kBarEmpty && bt < Plan::kBarFull) count = 4;
+            if (bt >= Plan::kBarFull && bt < Plan::kBarFree) count = Pol::kIsF8 ? 4 : 5;  // decoder warps (+ loader)
+            if (bt >= Plan::kBarXReady && bt < Plan::kBarXFree) count = kULoadWarps / kULoadTeams;
+            if (bt >= Plan::kBarXFree && bt < Plan::kBarDReady) count = NACC;
+            if (bt == Plan::kBarDReady) count = NACC;
+            if (bt == Plan::kBarDFree) count = 8;
+            mbar_init(bar(bt), count);
+            if (bt == 0) {
+                flags[0] = 0;
+                flags[1] = 0;
+            }
+            fence_mbar_init();
         }
-        fence_mbar_init();
+        if (warp == kUMmaWarp) tmem_alloc(smem_u32(const_cast<uint32_t *>(tmem_slot)), kUTmemCols);
+        if constexpr (!Pol::kIsF8) {  // fp16 stages: rows past the batch must read as zero
+            for (uint32_t o = ot * 16u; o < Plan::kXBytes; o += kOtherThreads * 16u) sts128(x_addr + o, make_uint4(0, 0, 0, 0));
+        }
+        fence_async_smem();
+        tc_fence_before();
+        if (ot == 0) DMM_STAMP(0, 2, 2);
+        if (bt == 0) DMM_STAMP(0, 3, 1);
+        named_barrier(3, kOtherThreads);
+        if (bt == 0) DMM_STAMP(0, 3, 2);
+        named_barrier_arrive(4, kUThreads);
+        if (bt == 0) DMM_STAMP(0, 2, 1);
     }
-    if (tid == 0) DMM_STAMP(0, 2, 1);
-    if (warp == kUMmaWarp) tmem_alloc(smem_u32(const_cast<uint32_t *>(tmem_slot)), kUTmemCols);
-    if constexpr (!Pol::kIsF8) {  // fp16 stages: rows past the batch must read as zero
-        for (uint32_t o = tid * 16u; o < Plan::kXBytes; o += kUThreads * 16u) sts128(x_addr + o, make_uint4(0, 0, 0, 0));
-    }
-    fence_async_smem();
-    tc_fence_before();
-    if (tid == 0) DMM_STAMP(0, 2, 2);
-    __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
     grid_dep_launch();
@@ -326,23 +359,14 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
 
     if (warp < kUDecWarps) {
         // =============================== decoders ===============================
+        // Nothing here reads what an earlier kernel of the stream wrote (codes and codebook are
+        // static), so the decoders never wait for it: they decode ahead into TMEM while the
+        // previous kernel drains; the activation loaders are the ones that wait.
         const int q = warp >> 2, wq = warp & 3;
         const uint32_t gring = ring_addr + static_cast<uint32_t>(q) * (RING * Plan::kSlotBytes);  // ring of group q
-        if (tid == 0) DMM_STAMP(0, 1, 0);
-
-        const bool bad = lut_fill(lut_addr, p.cb, 1, p.sign_convention, Pol::kFmt, tid, kUDecWarps * 32, Pol::kIsF8 != 0, &cb_pre);
-        if (bad) raise_status(DMM_STATUS_BAD_CODEBOOK);
-        if (tid == 0) DMM_STAMP(0, 1, 1);
-        if (lane == 0) DMM_STAMP(0, 8 + warp, 0);
-        named_barrier(1, kUDecWarps * 32);
+        if (bad_cb) raise_status(DMM_STATUS_BAD_CODEBOOK);
         const LutLane ll = lut_lane(lut_addr, lane, Pol::kIsF8 != 0);
-        grid_dep_wait();
         if (tid == 0) DMM_STAMP(0, 0, 2);
-        if (p.zero_ptr != nullptr) {  // a later kernel will accumulate into it
-            for (long long i = static_cast<long long>(cta) * (kUDecWarps * 32) + tid; i < p.zero_count;
-                 i += static_cast<long long>(gridDim.x) * (kUDecWarps * 32))
-                p.zero_ptr[i] = 0.f;
-        }
 
         const uint32_t tlane = tmem + (static_cast<uint32_t>(wq * 32) << 16);
         // The four groups share the shared-memory look-up pipe and are otherwise independent:
@@ -435,20 +459,39 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
                 float v[NB];
 #pragma unroll
                 for (int b = 0; b < NB; ++b) v[b] = 0.f;
+                if (Pol::kIsF8 && p.M == 1) {
+                    // batch 1: only column 8 * plane of every accumulator carries data; fetch those
+                    // sixteen words with one wait instead of whole accumulators one after the other
+                    uint32_t r[16];
 #pragma unroll
-                for (int a = 0; a < NACC; ++a) {
-                    if ((used >> a) & 1u) {
+                    for (int a = 0; a < 4; ++a) {
 #pragma unroll
-                        for (int b0 = 0; b0 < NMMA; b0 += 16) {
-                            uint32_t r[16];
-                            tmem_ld16(tlane + static_cast<uint32_t>((q * NACC + a) * NMMA + b0), r);
-                            tmem_wait_ld();
-                            // PolF8: column 8*plane + b; PolF16: column b
+                        for (int pl = 0; pl < 4; ++pl) {
+                            r[a * 4 + pl] = 0u;
+                            if (a < NACC && ((used >> a) & 1u))
+                                r[a * 4 + pl] = tmem_ld1(tlane + static_cast<uint32_t>((q * NACC + a) * NMMA + 8 * pl));
+                        }
+                    }
+                    tmem_wait_ld(r);
 #pragma unroll
-                            for (int e = 0; e < 16; ++e) v[(b0 + e) % NB] += __uint_as_float(r[e]);
+                    for (int e = 0; e < 16; ++e) v[0] += __uint_as_float(r[e]);
+                } else {
+#pragma unroll
+                    for (int a = 0; a < NACC; ++a) {
+                        if ((used >> a) & 1u) {
+#pragma unroll
+                            for (int b0 = 0; b0 < NMMA; b0 += 16) {
+                                uint32_t r[16];
+                                tmem_ld16(tlane + static_cast<uint32_t>((q * NACC + a) * NMMA + b0), r);
+                                tmem_wait_ld(r);
+                                // PolF8: column 8*plane + b; PolF16: column b
+#pragma unroll
+                                for (int e = 0; e < 16; ++e) v[(b0 + e) % NB] += __uint_as_float(r[e]);
+                            }
                         }
                     }
                 }
+                if (tid == 0) DMM_STAMP(4, segidx, 3);
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar(Plan::kBarDFree));
@@ -659,6 +702,12 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
         // loader wl serves the chunks of parity wl (the chunks of issuer wl), one chunk per pass
         grid_dep_wait();
         const int wl = warp - kUMmaWarp - kUMmaWarps;  // warps 20 .. 23
+        if (p.zero_ptr != nullptr) {  // a later kernel will accumulate into it
+            constexpr int ZT = kULoadWarps * 32;
+            for (long long i = static_cast<long long>(cta) * ZT + wl * 32 + lane; i < p.zero_count;
+                 i += static_cast<long long>(gridDim.x) * ZT)
+                p.zero_ptr[i] = 0.f;
+        }
         const __half *x = reinterpret_cast<const __half *>(p.x);
         const int M = static_cast<int>(p.M);
         const int ppt = M * 4;  // 16-byte pieces per k-tile: (row, 8-k chunk)

@@ -57,11 +57,29 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
+// try_wait that lets the hardware keep the thread suspended for up to `hint_ns` while the phase
+// is pending (it resumes as soon as the phase completes): a waiting warp then issues next to
+// nothing and leaves its scheduler to the warps that have work.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(hint_ns)
+        : "memory");
+    return ok != 0;
+}
+
 // Waits for a phase of an mbarrier, but never for longer than about a quarter of a second:
 // on expiry the CTA-wide `failed` flag is set, the device status word gets
 // DMM_STATUS_WAIT_TIMEOUT and every later wait of the CTA returns at once, so a lost
 // arrival produces a wrong result with a raised status instead of a hung GPU.
 constexpr long long kWaitLimitCycles = 500ll * 1000 * 1000;
+constexpr uint32_t kWaitHintNs = 20000;  // longest single suspension inside a wait
 
 __device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, volatile int *failed) {
     if (mbar_try_wait(bar, parity)) return;
@@ -72,7 +90,7 @@ __device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, volatil
         // looks at the clock so that a waiting warp costs almost no issue slots
 #pragma unroll 1
         for (int i = 0; i < 16; ++i)
-            if (mbar_try_wait(bar, parity)) return;
+            if (mbar_try_wait_hint(bar, parity, kWaitHintNs)) return;
         if (clock64() - t0 > kWaitLimitCycles || *failed) {
             if (!*failed) {
                 *failed = 1;

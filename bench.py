@@ -30,6 +30,10 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
+# DRAM bytes moved per algorithmic byte by the dominant kernel, from one ncu capture (see
+# profiles/umma_f8_57344x8192_b1.md): dram__bytes_read.sum + dram__bytes_write.sum = 121.84 MB
+# for 117.68 MB of codes, activations, output and codebook.
+NCU_TRAFFIC_PER_ALG_BYTE = 121.84 / 117.68
 METRIC = "compressed_weight_hbm_gbs"
 UNIT = "GB/s"
 
@@ -298,6 +302,7 @@ def run_ours(args):
         for blk in stack.layers:
             for lin in blk.values():
                 alg += lin.code_bytes + 2 * B * lin.in_features + 4 * B * lin.out_features + 4096
+        n_launch = sum(len(blk) for blk in stack.layers)
         peaks = {}
         try:
             peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
@@ -321,7 +326,12 @@ def run_ours(args):
             "roofline": {
                 "bound": "hbm", "achieved": achieved, "peak": peak,
                 "peak_source": "MEASURED_PEAKS.json hbm_gbs (of measured)" if peaks else "6650 GB/s (of fallback)",
-                "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                "unit": "GB/s", "frac": achieved / peak,
+                "traffic": NCU_TRAFFIC_PER_ALG_BYTE * alg / n_launch if B <= 8 else None,
+                "traffic_unit": "bytes per launch (mean over the stack's launches)",
+                "traffic_source": "ncu capture of the 57344x8192 launch (profiles/umma_f8_57344x8192_b1.md): "
+                                  "121.84 MB DRAM read+write for 117.68 MB algorithmic; scaled by algorithmic bytes",
+                "algorithmic_bytes_per_launch": alg / n_launch,
                 "kernel": "umma_kernel<PolF8,32>" if B <= 8 else "umma_kernel<PolF16,*>",
                 "how": "all matmul launches of the stack back to back in one CUDA graph, CUDA events; per-GPU figure",
                 "ms": ms_kernels,

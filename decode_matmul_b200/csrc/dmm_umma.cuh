@@ -7,7 +7,7 @@
 //
 // Two operand policies share the kernel:
 //   PolF8   (batch <= 8)  weights as fp6 E2M3 bytes (sign << 5 | |q|, value q/8: exact, and
-//                         produced by the table XOR alone, 6 instructions per code), the
+//                         produced by the table XOR alone, 7 instructions per code), the
 //                         fp16 activations split EXACTLY into four E5M2 planes (the top byte
 //                         of the half, then of the remainder, ...), kind::f8f6f4, K = 32.
 //                         The four planes are stacked along the MMA n dimension (n = 8*plane
@@ -24,17 +24,21 @@
 // numbered super-tile-major and split evenly and contiguously over the CTAs (stream-K); the
 // part of a super-tile a CTA owns is a segment.
 //
-// Warp roles (23 warps):
-//   0..15  decoders, four groups of four warps.  Group q takes chunks q, q+4, ... (C tiles
-//          each) of a segment.  Warp wq of a group owns TMEM lanes 32wq..32wq+31 = strips
-//          4wq..4wq+3; it streams its own strips through a private TMA ring, decodes, writes
-//          A stage buffers in TMEM and signals its MMA issuer.  Groups 0 and 1 also run the
-//          epilogue of tile 0 and tile 1.
-//   16..19 MMA issuers (one elected thread each); issuer s serves the decoder groups q with
-//          q % kNAcc == s and owns accumulator s of both MMA tiles.  Warp 16 also allocates
-//          the tensor memory.
-//   20..21 activation loaders.
-//   22     TMA producer (one thread): streams the code chunks into the groups' rings.
+// Warp roles (25 warps):
+//   0..15  decoders, four groups of four warps.  Group q takes the chunks whose CTA-wide number
+//          is q mod 4 (C k-tiles of 16 strips each).  Warp wq of a group owns TMEM lanes
+//          32wq..32wq+31 = strips 4wq..4wq+3; it reads its strips from the group's code ring,
+//          decodes, writes A stage buffers in TMEM and signals the group's MMA issuer.  The
+//          decoders also build the look-up table at the start, and groups 0 and 1 run the
+//          epilogue of MMA tile 0 and tile 1.
+//   16..19 MMA issuers (converged warp, one elected lane issues); issuer s serves the decoder
+//          groups q with q % kNAcc == s and owns accumulator s of both MMA tiles (fp8 policy:
+//          one issuer per group).  Warp 16 also allocates the tensor memory.
+//   20..23 activation loaders (fp8 policy: two teams filling alternate epochs of E5M2 planes;
+//          fp16 policy: warps 20 and 21 stage the chunks with cp.async).  They are the only
+//          warps that wait for the previous kernel of the stream.
+//   24     TMA producer (one thread): streams the code chunks into the groups' rings, one
+//          tiled bulk-tensor load per chunk.
 // Every wait is bounded (mbar_wait); nothing spins on another CTA.
 #pragma once
 #include <cuda.h>

@@ -277,7 +277,7 @@ def run_ours(args):
     def kernels_only():  # same launch mode as the step: PDL chain, atomic accumulation for small batch
         for blk in stack.layers:
             for k, lin in blk.items():
-                if B <= 8:
+                if B <= 32:
                     dmm.decode_matmul_fp16(xs[k], lin.codes, lin.codebook, lin.scale, outs[k], accumulate=True,
                                            atomic=True, pdl=True)
                 else:
@@ -332,7 +332,7 @@ def run_ours(args):
                 "traffic_source": "ncu capture of the 57344x8192 launch (profiles/umma_f8_57344x8192_b1.md): "
                                   "121.84 MB DRAM read+write for 117.68 MB algorithmic; scaled by algorithmic bytes",
                 "algorithmic_bytes_per_launch": alg / n_launch,
-                "kernel": "umma_kernel<PolF8,32>" if B <= 8 else "umma_kernel<PolF16,*>",
+                "kernel": "umma_kernel<PolF8,32>" if B <= 8 else ("umma_kernel<PolF8,64>" if B <= 16 else "umma_kernel<PolF8,128>"),
                 "how": "all matmul launches of the stack back to back in one CUDA graph, CUDA events; per-GPU figure",
                 "ms": ms_kernels,
             },

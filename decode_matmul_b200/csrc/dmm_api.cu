@@ -45,20 +45,27 @@ static size_t ticket_bytes(long long N) {
 }
 
 // Every path shares the ticket block; the partial block is sized for the widest path
-// that a batch of M columns can take (tcgen05, fp16 operands).
-static size_t workspace_need(long long M, long long N, int num_sms) {
+// that a batch of M columns can take (tcgen05, fp16 operands); behind it sits the buffer of
+// pre-split activation planes of the fp8-operand path (up to 32 padded rows x K x 4 planes).
+static size_t partial_bytes(long long M, int num_sms) {
     size_t per_slot = kPartialValues;
     const size_t umma = static_cast<size_t>(umma_partial_values(M > 64 ? 64 : M, false));
     if (umma > per_slot) per_slot = umma;
-    return ticket_bytes(N) + static_cast<size_t>(num_sms) * 2 * per_slot * 4;
+    return static_cast<size_t>(num_sms) * 2 * per_slot * 4;
+}
+static size_t planes_offset(long long M, long long N, int num_sms) {
+    return (ticket_bytes(N) + partial_bytes(M, num_sms) + 255) & ~static_cast<size_t>(255);
+}
+static size_t workspace_need(long long M, long long N, long long K, int num_sms) {
+    return planes_offset(M, N, num_sms) + static_cast<size_t>(K) * 128;
 }
 
 // Returns the workspace to use: the caller's (checked for size) or the library's own,
 // grown on demand.  The ticket counters must be zero before the first launch; the
 // library's buffer is cleared when it is (re)allocated, a caller's buffer by the caller.
-static int resolve_workspace(DeviceState *d, long long M, long long N, void *user, size_t user_bytes,
+static int resolve_workspace(DeviceState *d, long long M, long long N, long long K, void *user, size_t user_bytes,
                              cudaStream_t stream, void **ws) {
-    const size_t need = workspace_need(M, N, d->num_sms);
+    const size_t need = workspace_need(M, N, K, d->num_sms);
     if (user != nullptr) {
         if (user_bytes < need) return DMM_ERR_WORKSPACE;
         if (reinterpret_cast<uintptr_t>(user) % 256 != 0) return DMM_ERR_ALIGN;
@@ -106,7 +113,7 @@ static int run_stream(int family, const void *x, const void *codes, const void *
     int rc = current_device_state(&d);
     if (rc) return rc;
     void *ws = nullptr;
-    rc = resolve_workspace(d, M, N, workspace, workspace_bytes, stream, &ws);
+    rc = resolve_workspace(d, M, N, K, workspace, workspace_bytes, stream, &ws);
     if (rc) return rc;
     const size_t x_elem = family == 0 ? 1 : 2;
     for (long long m0 = 0; m0 < M; m0 += 16) {
@@ -135,7 +142,8 @@ static int run_stream(int family, const void *x, const void *codes, const void *
 static long long *g_trace = nullptr;  // device buffer for clock stamps (debug builds only)
 #endif
 
-// tcgen05 path: one launch per chunk of 64 batch columns (8 for the fp6/fp8 operand policy).
+// tcgen05 path: one launch per chunk of 64 batch columns (32 for the fp6/fp8 operand policy,
+// preceded by planes_kernel when the chunk has at least kPlanesMinBatch rows).
 static int run_umma(bool f8, const void *x, int x_kind, long long x_ld, long long x_gap, const void *codes,
                     const void *cb16, float scale, float *out, long long M, long long N, long long K,
                     int sign_convention, unsigned flags, void *workspace, size_t workspace_bytes, cudaStream_t stream,
@@ -144,12 +152,22 @@ static int run_umma(bool f8, const void *x, int x_kind, long long x_ld, long lon
     int rc = current_device_state(&d);
     if (rc) return rc;
     void *ws = nullptr;
-    rc = resolve_workspace(d, M, N, workspace, workspace_bytes, stream, &ws);
+    rc = resolve_workspace(d, M, N, K, workspace, workspace_bytes, stream, &ws);
     if (rc) return rc;
-    const long long step = f8 ? 8 : 64;
+    const long long step = f8 ? 32 : 64;
+    const bool pdl = (flags & DMM_FLAG_PDL) != 0;
     for (long long m0 = 0; m0 < M; m0 += step) {
         UmmaParams p = {};
         p.x = reinterpret_cast<const uint8_t *>(x) + static_cast<size_t>(m0) * x_ld * (x_kind == DMM_X_F16 ? 2 : 4);
+        p.M = M - m0 < step ? M - m0 : step;
+        if (f8 && p.M >= kPlanesMinBatch) {
+            // split the activations into E5M2 planes once, instead of once per CTA inside the kernel
+            uint8_t *planes = reinterpret_cast<uint8_t *>(ws) + planes_offset(M, N, d->num_sms);
+            rc = launch_planes(p.x, x_kind, x_ld, x_gap, static_cast<int>(p.M), K, planes, pdl, stream);
+            g_launches.fetch_add(1, std::memory_order_relaxed);
+            if (rc) return rc;
+            p.x_planes = planes;
+        }
         p.x_mode = x_kind;
         p.x_ld = x_ld;
         p.x_gap = x_gap;
@@ -158,7 +176,6 @@ static int run_umma(bool f8, const void *x, int x_kind, long long x_ld, long lon
         p.out = out + static_cast<size_t>(m0) * N;
         p.tickets = reinterpret_cast<unsigned *>(ws);
         p.partials = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(ws) + ticket_bytes(N));
-        p.M = M - m0 < step ? M - m0 : step;
         p.N = N;
         p.K = K;
         // accumulators hold sum(x * q / 8) (fp6 weights) or sum(x * q) (fp16 weights); weight = q / 4
@@ -173,7 +190,7 @@ static int run_umma(bool f8, const void *x, int x_kind, long long x_ld, long lon
 #ifdef DMM_TRACE
         p.trace = g_trace;
 #endif
-        rc = launch_umma(f8, p, d->num_sms, (flags & DMM_FLAG_PDL) != 0, stream);
+        rc = launch_umma(f8, p, d->num_sms, pdl, stream);
         g_launches.fetch_add(1, std::memory_order_relaxed);
         if (rc) return rc;
     }
@@ -322,7 +339,7 @@ size_t dmm_workspace_bytes(int64_t M, int64_t N, int64_t K) {
     DeviceState *d = nullptr;
     int sms = 256;
     if (current_device_state(&d) == 0 && d->num_sms > 0) sms = d->num_sms;
-    return workspace_need(M, N, sms);
+    return workspace_need(M, N, K, sms);
 }
 
 int dmm_status(unsigned *status_out) {
@@ -340,9 +357,12 @@ int dmm_status(unsigned *status_out) {
 }
 
 int dmm_select_path(int64_t M, int64_t N, int64_t K) {
+    // Measured on B200: the fp6/fp8-operand kernel (32 batch rows per pass, planes split once by
+    // planes_kernel from 4 rows on) beats the fp16-operand one at every batch size.
+    (void)M;
     (void)N;
     (void)K;
-    return M <= 8 ? DMM_PATH_TCGEN05_F8 : DMM_PATH_TCGEN05;
+    return DMM_PATH_TCGEN05_F8;
 }
 
 uint64_t dmm_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }

@@ -121,6 +121,13 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t
         : "memory");
 }
 
+// The same without a cache hint (data that other CTAs read again from L2).
+__device__ __forceinline__ void bulk_g2s_plain(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
 // 2-D tiled TMA load (tensor map in kernel parameter space), completion counted on an mbarrier.
 // x is in elements of the map's data type and x * element size must be a multiple of 16 bytes.
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const void *tmap, int x, int y, uint32_t bar,

@@ -121,6 +121,15 @@ __device__ __forceinline__ void mma_ts_f8(uint32_t d, uint32_t a, uint64_t bdesc
         "r"(a), "l"(bdesc), "r"(idesc), "r"(acc)
         : "memory");
 }
+// The same with the descriptor as two 32-bit words (only the low word changes from tile to tile).
+__device__ __forceinline__ void mma_ts_f8_lh(uint32_t d, uint32_t a, uint32_t desc_lo, uint32_t desc_hi, uint32_t idesc,
+                                             uint32_t acc) {
+    asm volatile(
+        "{\n.reg .pred p;\n.reg .b64 bd;\nsetp.ne.b32 p, %5, 0;\nmov.b64 bd, {%2, %3};\n"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%1], bd, %4, p;\n}\n" ::"r"(d),
+        "r"(a), "r"(desc_lo), "r"(desc_hi), "r"(idesc), "r"(acc)
+        : "memory");
+}
 // Shared-memory operand descriptor, no swizzle, K-major: 8-row x 16-byte core matrices;
 // lbo = byte distance between core matrices along K, sbo = between 8-row groups.
 __device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo, uint32_t sbo) {
@@ -159,7 +168,7 @@ struct PolF8 {
     static constexpr int kRing = 3;    // chunks in flight per decoder group
     static constexpr int kACols = 8;   // TMEM columns of one k-tile of one MMA tile (32 k x 1 byte)
     static constexpr uint32_t x_tile_bytes(int) { return 1024; }  // 2 k-halves x (4 planes x 8 rows) x 16 B
-    static constexpr int out_cols(int) { return 8; }                // batch columns per launch
+    static constexpr int out_cols(int nmma) { return nmma / 4; }    // batch columns per launch: 8 or 16
 };
 struct PolF16 {
     static constexpr int kIsF8 = 0;
@@ -186,6 +195,14 @@ __host__ __device__ inline int first_epoch_tiles(int E, int M) {
     return e0 < E ? e0 : E;
 }
 
+// Bytes of the E5M2 planes of one k-tile: [k-half][plane][row][16 B].  Up to 8 batch rows the
+// rows of a plane are packed densely (M rows); the 64- and 128-column variants pad a plane to 16
+// and 32 rows.
+template <int NMMA>
+__host__ __device__ inline uint32_t plane_tile_bytes(int M) {
+    return 128u * static_cast<uint32_t>(NMMA > 64 ? 32 : (NMMA > 32 ? 16 : M));
+}
+
 // k-tiles per activation epoch: what fits in one epoch buffer, even, at most kMaxEpoch
 __host__ __device__ inline int epoch_tiles(uint32_t epoch_bytes, uint32_t tile_bytes) {
     const int fit = static_cast<int>((epoch_bytes / tile_bytes) & ~1u);
@@ -196,7 +213,12 @@ constexpr uint32_t kUTmemCols = 512;
 
 template <class Pol, int NMMA>
 struct UmmaPlan {
-    static constexpr int kNAcc = Pol::kIsF8 ? 4 : 2;              // accumulators per MMA tile = active issuers
+    // accumulators per MMA tile = active issuers: one per decoder group while the TMEM holds them
+    static constexpr int kNAcc = !Pol::kIsF8 ? 2 : (NMMA <= 32 ? 4 : (NMMA <= 64 ? 2 : 1));
+    // issuer warps per accumulator: with fewer than four accumulators the two MMA tiles of a
+    // group are issued by different warps (each accumulator still has exactly one issuer, so the
+    // summation order stays fixed)
+    static constexpr int kTileParts = kNAcc <= 2 ? 2 : 1;
     static constexpr uint32_t kDCols = 2 * kNAcc * NMMA;          // TMEM: accumulators first
     static constexpr uint32_t kBufCols = 2 * Pol::kG * Pol::kACols;  // one group buffer: [tile][k-tile][cols]
     static constexpr uint32_t kACols = 4 * Pol::kNA * kBufCols;
@@ -205,8 +227,12 @@ struct UmmaPlan {
     static constexpr uint32_t kXStage = Pol::kG * Pol::x_tile_bytes(NMMA);
     // fp8 policy: the activation planes of a whole run of k-tiles ("epoch") stay resident in one
     // of kEpochs buffers, densely packed [tile][k-half][plane][row < M][16 B]
-    static constexpr int kEpochs = 4;
-    static constexpr uint32_t kEpochBytes = 14336;
+    // (128 columns = 32 batch rows: a k-tile of planes is 4 KiB, so more and smaller buffers)
+#ifndef DMM_EPOCHS128
+#define DMM_EPOCHS128 7
+#endif
+    static constexpr int kEpochs = NMMA > 64 ? DMM_EPOCHS128 : 4;
+    static constexpr uint32_t kEpochBytes = NMMA > 64 ? 8192 : 14336;
     static constexpr uint32_t kXBytes = Pol::kIsF8 ? kEpochs * kEpochBytes + 256 : kSlots * kXStage;
     static constexpr int kNB = Pol::out_cols(NMMA);               // output columns per launch
     static constexpr uint32_t kPreBytes = kUBarBytes + kXBytes;
@@ -249,6 +275,9 @@ struct UmmaParams {
     int atomic_reduce;   // partial super-tiles are added to `out` with red.global.add (out must hold the
                          // value to add to): no workspace round trip, summation order not fixed
     int sign_convention;
+    const void *x_planes;  // fp8 policy, optional: the E5M2 planes of x already split by planes_kernel, in the
+                           // layout of the epoch buffers ([k-tile][k-half][plane][row][16 B]); the
+                           // kernel then copies them with bulk copies and its loaders do no arithmetic
     float *zero_ptr;     // optional: buffer this kernel clears on its way (see dmm_f16_fused)
     long long zero_count;
     Part32 part;         // tiles per CTA: part.a = T / grid, part.b = T % grid
@@ -265,6 +294,68 @@ struct UmmaParams {
 #define DMM_STAMP(role, idx, what) do { } while (0)
 #endif
 
+// Eight consecutive activations of one row as four packed half2 words, from any input kind.
+__device__ __forceinline__ void load_piece(const void *xp, int x_mode, long long x_ld, long long x_gap, int row,
+                                           long long k0, uint32_t (&h)[4]) {
+    if (x_mode == kXHalf) {
+        const uint4 v = __ldg(reinterpret_cast<const uint4 *>(reinterpret_cast<const __half *>(xp) + row * x_ld + k0));
+        h[0] = v.x; h[1] = v.y; h[2] = v.z; h[3] = v.w;
+        return;
+    }
+    const float *xf = reinterpret_cast<const float *>(xp) + row * x_ld + k0;
+    const float4 a0 = __ldcg(reinterpret_cast<const float4 *>(xf));
+    const float4 a1 = __ldcg(reinterpret_cast<const float4 *>(xf + 4));
+    float f[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+    if (x_mode == kXSiluMul) {
+        const float4 b0 = __ldcg(reinterpret_cast<const float4 *>(xf + x_gap));
+        const float4 b1 = __ldcg(reinterpret_cast<const float4 *>(xf + x_gap + 4));
+        const float g[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+        for (int j = 0; j < 8; ++j) f[j] = __fdividef(f[j], 1.0f + __expf(-f[j])) * g[j];
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const __half2 hh = __floats2half2_rn(f[2 * j], f[2 * j + 1]);
+        h[j] = *reinterpret_cast<const uint32_t *>(&hh);
+    }
+}
+
+// Plane `pl` of a piece = the top byte of each half (an E5M2 number: truncation of the half);
+// returns its eight bytes and leaves the exact remainder in h for the next plane.
+__device__ __forceinline__ uint2 next_plane(uint32_t (&h)[4]) {
+    const uint2 bytes = make_uint2(prmt(h[0], h[1], 0x7531u), prmt(h[2], h[3], 0x7531u));
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const uint32_t top = h[j] & 0xFF00FF00u;
+        __half2 rr = __hsub2(*reinterpret_cast<__half2 *>(&h[j]), *reinterpret_cast<const __half2 *>(&top));
+        h[j] = *reinterpret_cast<uint32_t *>(&rr);
+    }
+    return bytes;
+}
+
+// Splits the activations of one call into E5M2 planes ONCE, in the layout the tcgen05 kernel's
+// epoch buffers use: [k-tile][k-half][plane][row < rows_padded][16 B].  With more than a few
+// batch rows the per-CTA split inside umma_kernel (every CTA repeats it for its k range) costs
+// more than the decode itself; this kernel does it once and umma_kernel then only copies.
+// One thread per piece (8 k of one row); thread order (k-tile, k-half, row, half) so that the
+// stores of a warp are contiguous per plane.
+__global__ void __launch_bounds__(128) planes_kernel(const void *x, int x_mode, long long x_ld, long long x_gap, int M,
+                                                     long long K, int rows_padded, uint8_t *planes) {
+    grid_dep_wait();  // x is the previous kernel's output; the buffer may still be read by the kernel before it
+    grid_dep_launch();
+    const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const int per_half = 2 * M;  // pieces per (k-tile, k-half)
+    const long long kh_idx = idx / per_half;
+    if (kh_idx >= K / 16) return;
+    const int rem = static_cast<int>(idx - kh_idx * per_half), row = rem >> 1, half = rem & 1;
+    uint32_t h[4];
+    load_piece(x, x_mode, x_ld, x_gap, row, kh_idx * 16 + half * 8, h);
+    const uint32_t tile_b = 128u * static_cast<uint32_t>(rows_padded);
+    uint8_t *dst = planes + kh_idx * (tile_b / 2) + row * 16 + half * 8;
+#pragma unroll
+    for (int pl = 0; pl < 4; ++pl) *reinterpret_cast<uint2 *>(dst + pl * (tile_b / 8)) = next_plane(h);
+}
+
 // `codes_map` is a 2-D tensor map of the tiled code matrix: inner dimension = one strip
 // (K/32 k-tiles x 32 uint32), outer dimension = strips; box = kC k-tiles x 16 strips.
 template <class Pol, int NMMA>
@@ -272,6 +363,7 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
                                                             const __grid_constant__ CUtensorMap codes_map) {
     using Plan = UmmaPlan<Pol, NMMA>;
     constexpr int C = Pol::kC, G = Pol::kG, NA = Pol::kNA, RING = Pol::kRing, NACC = Plan::kNAcc, NB = Plan::kNB;
+    constexpr int TP = Plan::kTileParts;
 
     extern __shared__ __align__(1024) uint8_t smem_raw[];
     const uint32_t base = smem_u32(smem_raw);
@@ -282,7 +374,9 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
     volatile uint32_t *tmem_slot = reinterpret_cast<volatile uint32_t *>(smem_raw + Plan::kBarCount * 8 + 16);
     auto bar = [&](int i) -> uint32_t { return base + 8u * static_cast<uint32_t>(i); };
 
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // the warp index through a shuffle: the compiler then knows it is the same in every lane and
+    // keeps what derives from it (roles, descriptors, TMEM addresses) in uniform registers
+    const int tid = threadIdx.x, warp = __shfl_sync(0xffffffffu, tid >> 5, 0), lane = tid & 31;
     if (tid == 0) DMM_STAMP(0, 0, 0);
     const uint4 cb_pre = lut_prefetch(p.cb, tid);  // the codebook is static data: fetch it first
 
@@ -332,9 +426,10 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
             uint32_t count = 1;                                                // TMA, tcgen05.commit
             if (bt >= Plan::kBarEmpty && bt < Plan::kBarFull) count = 4;
             if (bt >= Plan::kBarFull && bt < Plan::kBarFree) count = Pol::kIsF8 ? 4 : 5;  // decoder warps (+ loader)
-            if (bt >= Plan::kBarXReady && bt < Plan::kBarXFree) count = kULoadWarps / kULoadTeams;
-            if (bt >= Plan::kBarXFree && bt < Plan::kBarDReady) count = NACC;
-            if (bt == Plan::kBarDReady) count = NACC;
+            if (bt >= Plan::kBarXReady && bt < Plan::kBarXFree) count = p.x_planes != nullptr ? 1 : kULoadWarps / kULoadTeams;
+            if (bt >= Plan::kBarFree && bt < Plan::kBarXReady) count = TP;  // tcgen05.commit of every issuer of the slot
+            if (bt >= Plan::kBarXFree && bt < Plan::kBarDReady) count = NACC * TP;
+            if (bt == Plan::kBarDReady) count = NACC * TP;
             if (bt == Plan::kBarDFree) count = 8;
             mbar_init(bar(bt), count);
             if (bt == 0) {
@@ -357,7 +452,7 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
         if (bt == 0) DMM_STAMP(0, 2, 1);
     }
     tc_fence_after();
-    const uint32_t tmem = *tmem_slot;
+    const uint32_t tmem = __shfl_sync(0xffffffffu, *tmem_slot, 0);
     grid_dep_launch();
     if (tid == 0) DMM_STAMP(0, 0, 1);
 
@@ -578,31 +673,28 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
         // issuer `me` serves the decoder groups q with q % kNAcc == me and owns accumulator `me`
         // The whole warp runs the loop converged (so that addresses and descriptors stay in
         // uniform registers); one elected lane issues the tcgen05 instructions.
-        const int me = warp - kUMmaWarp;
-        if (me < NACC) {
+        const int wi = warp - kUMmaWarp;
+        const int me = wi % NACC;  // accumulator (and decoder groups q % NACC == me) this warp serves
+        const int tp = wi / NACC;  // which MMA tile of a group it issues when the tiles are split (TP == 2)
+        const int t_lo = TP == 2 ? tp : 0, t_hi = TP == 2 ? tp + 1 : 2;
+        if (wi < NACC * TP) {
             const bool leader = elect_one();
-            uint32_t cnt0 = 0, cnt1 = 0;  // groups consumed from decoder groups me and me + 2
+            uint32_t cnt0 = 0, cnt1 = 0, cnt2 = 0, cnt3 = 0;  // groups consumed from decoder group 0..3
             int segidx = 0;
             const uint32_t idesc = Pol::kIsF8
                                        ? ((1u << 4) | (3u << 7) | (1u << 10) | ((NMMA >> 3) << 17) | ((128u >> 4) << 24))
                                        : ((1u << 4) | ((NMMA >> 3) << 17) | ((128u >> 4) << 24));
             // descriptor of activation stage 0; later stages and k-halves only move the address field
-            const uint32_t tile_b = 128u * static_cast<uint32_t>(p.M);  // fp8: bytes of one k-tile of planes
+            const uint32_t tile_b = plane_tile_bytes<NMMA>(static_cast<int>(p.M));  // fp8: bytes of one k-tile of planes
             const int E = epoch_tiles(Plan::kEpochBytes, tile_b);  // k-tiles per epoch
             const int E0 = first_epoch_tiles(E, static_cast<int>(p.M));           // the first one is short
-            const uint64_t xdesc0 = Pol::kIsF8 ? smem_desc(x_addr, tile_b / 2, tile_b / 8) : smem_desc(x_addr, NMMA * 16, 128);
+            // fp8: a plane is one 8-row core matrix (rows past the batch overlap the next plane and
+            // land in unused columns) or, for the 16-row layout, two of them
+            const uint64_t xdesc0 = Pol::kIsF8 ? smem_desc(x_addr, tile_b / 2, NMMA > 32 ? 128u : tile_b / 8)
+                                               : smem_desc(x_addr, NMMA * 16, 128);
             int cur_ep = -1, ep_beg = 0, ep_end = 0;  // fp8: epoch being read and its k-tile range
             uint32_t ep_addr = 0;
-            auto enter_epoch = [&](int e) {
-                // every earlier epoch is finished for this issuer: let the loaders reuse its buffer
-                for (int r = cur_ep < 0 ? 0 : cur_ep; r < e; ++r)
-                    if (leader) tc_commit(bar(Plan::kBarXFree + r % Plan::kEpochs));
-                mbar_wait(bar(Plan::kBarXReady + e % Plan::kEpochs), static_cast<uint32_t>((e / Plan::kEpochs) & 1), flags);
-                cur_ep = e;
-                ep_beg = e == 0 ? 0 : E0 + (e - 1) * E;
-                ep_end = E0 + e * E;
-                ep_addr = ((e % Plan::kEpochs) * Plan::kEpochBytes) >> 4;
-            };
+            const uint32_t xdesc_lo = static_cast<uint32_t>(xdesc0), xdesc_hi = static_cast<uint32_t>(xdesc0 >> 32);
             int cbase = 0, jseg = 0;  // chunks / k-tiles of earlier segments
             for (int ss = ss_first; ss <= ss_last; cbase += seg_chunks(ss), jseg += seg_len(ss), ++ss, ++segidx) {
                 const int len = seg_len(ss);
@@ -617,35 +709,48 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
                     const int n = len - c * C < C ? len - c * C : C;
 #pragma unroll 1
                     for (int g0 = 0; g0 < n; g0 += G) {
-                        const uint32_t cn = q < 2 ? cnt0 : cnt1;
+                        const uint32_t cn = q == 0 ? cnt0 : q == 1 ? cnt1 : q == 2 ? cnt2 : cnt3;
                         const int sl = q * NA + static_cast<int>(cn % NA);
-                        if (me == 0 && leader) DMM_STAMP(2, cn * 2 + (q >> 1), 0);
-                        mbar_wait(bar(Plan::kBarFull + sl), (cn / NA) & 1, flags);
-                        tc_fence_after();
-                        if (me == 0 && leader) DMM_STAMP(2, cn * 2 + (q >> 1), 1);
-                        const uint64_t xd = xdesc0 + ((static_cast<uint32_t>(sl) * Plan::kXStage) >> 4);
+                        if (wi == 0 && leader) DMM_STAMP(2, cn * 2 + (q >> 1), 0);
                         const uint32_t a_col = tmem + Plan::kDCols + static_cast<uint32_t>(sl) * Plan::kBufCols;
                         if constexpr (Pol::kIsF8) {
+                            mbar_wait(bar(Plan::kBarFull + sl), (cn / NA) & 1, flags);
+                            tc_fence_after();
+                            if (wi == 0 && leader) DMM_STAMP(2, cn * 2 + (q >> 1), 1);
                             // tile by tile (both MMA tiles of a k-tile back to back), so that an
                             // epoch is only left when nothing issued later still reads its buffer
 #pragma unroll
                             for (int i = 0; i < G; ++i) {
                                 if (g0 + i < n) {
                                     const int jt = jseg + c * C + g0 + i;  // CTA-wide k-tile index
-                                    if (jt >= ep_end) enter_epoch(jt < E0 ? 0 : 1 + (jt - E0) / E);
-                                    const uint64_t xt = xdesc0 + ep_addr + ((static_cast<uint32_t>(jt - ep_beg) * tile_b) >> 4);
+                                    if (jt >= ep_end) {
+                                        // step to the epoch that holds jt (no division: an issuer only moves forward)
+                                        int e = cur_ep < 0 ? 0 : cur_ep;
+                                        while (jt >= E0 + e * E) {
+                                            if (leader) tc_commit(bar(Plan::kBarXFree + e % Plan::kEpochs));  // also epochs it never read
+                                            ++e;
+                                        }
+                                        mbar_wait(bar(Plan::kBarXReady + e % Plan::kEpochs), static_cast<uint32_t>((e / Plan::kEpochs) & 1), flags);
+                                        cur_ep = e;
+                                        ep_beg = e == 0 ? 0 : E0 + (e - 1) * E;
+                                        ep_end = E0 + e * E;
+                                        ep_addr = ((e % Plan::kEpochs) * Plan::kEpochBytes) >> 4;
+                                    }
+                                    const uint32_t xlo = xdesc_lo + ep_addr + ((static_cast<uint32_t>(jt - ep_beg) * tile_b) >> 4);
                                     const uint32_t acc = (first && i == 0) ? 0u : 1u;
                                     if (leader) {
-#pragma unroll
-                                        for (int t = 0; t < 2; ++t)
-                                            mma_ts_f8(tmem + static_cast<uint32_t>((t * NACC + me) * NMMA),
-                                                      a_col + (t * G + i) * Pol::kACols, xt, idesc, acc);
+                                        for (int t = t_lo; t < t_hi; ++t)
+                                            mma_ts_f8_lh(tmem + static_cast<uint32_t>((t * NACC + me) * NMMA),
+                                                         a_col + (t * G + i) * Pol::kACols, xlo, xdesc_hi, idesc, acc);
                                     }
                                 }
                             }
                         } else {
-#pragma unroll
-                            for (int t = 0; t < 2; ++t) {
+                            mbar_wait(bar(Plan::kBarFull + sl), (cn / NA) & 1, flags);
+                            tc_fence_after();
+                            if (wi == 0 && leader) DMM_STAMP(2, cn * 2 + (q >> 1), 1);
+                            const uint64_t xd = xdesc0 + ((static_cast<uint32_t>(sl) * Plan::kXStage) >> 4);
+                            for (int t = t_lo; t < t_hi; ++t) {
                                 const uint32_t d_col = tmem + static_cast<uint32_t>((t * NACC + me) * NMMA);
                                 if (leader) {
                                     mma_ts_f16(d_col, a_col + t * G * Pol::kACols, xd, idesc, first ? 0u : 1u);
@@ -655,8 +760,8 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
                         }
                         first = false;
                         if (leader) tc_commit(bar(Plan::kBarFree + sl));
-                        if (me == 0 && leader) DMM_STAMP(2, cn * 2 + (q >> 1), 2);
-                        if (q < 2) ++cnt0; else ++cnt1;
+                        if (wi == 0 && leader) DMM_STAMP(2, cn * 2 + (q >> 1), 2);
+                        if (q == 0) ++cnt0; else if (q == 1) ++cnt1; else if (q == 2) ++cnt2; else ++cnt3;
                     }
                 }
                 if (leader) tc_commit(bar(Plan::kBarDReady));
@@ -712,7 +817,7 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
                  i += static_cast<long long>(gridDim.x) * ZT)
                 p.zero_ptr[i] = 0.f;
         }
-        const __half *x = reinterpret_cast<const __half *>(p.x);
+        [[maybe_unused]] const __half *x = reinterpret_cast<const __half *>(p.x);
         const int M = static_cast<int>(p.M);
         const int ppt = M * 4;  // 16-byte pieces per k-tile: (row, 8-k chunk)
         uint32_t cnt0 = 0, cnt1 = 0;  // groups staged so far for decoder groups wl and wl + 2
@@ -724,7 +829,7 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
             // densely packed [tile][k-half][plane][row][16 B]; the issuers point their operand
             // descriptors straight into these buffers.  A piece is 8 consecutive k of one row.
             constexpr int U = 4;  // pieces in flight per thread
-            const uint32_t tile_b = 128u * static_cast<uint32_t>(M);
+            const uint32_t tile_b = plane_tile_bytes<NMMA>(M);
             const int E = epoch_tiles(Plan::kEpochBytes, tile_b);
             // The first epoch is short: nothing can be multiplied before it is staged, and the
             // loaders may only start once the previous kernel of the stream has finished.
@@ -733,10 +838,37 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
             const int nep = ntiles <= E0 ? 1 : 1 + (ntiles - E0 + E - 1) / E;
             // two teams of loader warps fill alternate epochs, so that the global-memory latency
             // of one epoch overlaps the plane split of the other
+            if (p.x_planes != nullptr && wl == 0 && lane == 0) {
+                // The planes were split once by planes_kernel: an epoch is one bulk copy per
+                // contiguous run of k-tiles (two when the CTA's tile sequence wraps to the next
+                // super-tile inside the epoch).
+                const uint8_t *src = reinterpret_cast<const uint8_t *>(p.x_planes);
+                for (int e = 0; e < nep; ++e) {
+                    if (e >= Plan::kEpochs)
+                        mbar_wait(bar(Plan::kBarXFree + e % Plan::kEpochs), static_cast<uint32_t>(((e / Plan::kEpochs) - 1) & 1), flags);
+                    const int t_lo = e == 0 ? 0 : E0 + (e - 1) * E;
+                    const int e_len = e == 0 ? E0 : E;
+                    const int nt = ntiles - t_lo < e_len ? ntiles - t_lo : e_len;
+                    const uint32_t ebuf = x_addr + (e % Plan::kEpochs) * Plan::kEpochBytes;
+                    const uint32_t b = bar(Plan::kBarXReady + e % Plan::kEpochs);
+                    mbar_arrive_expect_tx(b, static_cast<uint32_t>(nt) * tile_b);
+                    for (int t = 0; t < nt;) {
+                        const int gt = i0 + t_lo + t;
+                        const int kt = gt - (gt / KT) * KT;
+                        const int run = KT - kt < nt - t ? KT - kt : nt - t;
+                        bulk_g2s_plain(ebuf + t * tile_b, src + static_cast<size_t>(kt) * tile_b, static_cast<uint32_t>(run) * tile_b, b);
+                        t += run;
+                    }
+                }
+                if (flags[0]) {  // a wait gave up: let the copies in flight land before the CTA exits
+                    for (int e = nep > Plan::kEpochs ? nep - Plan::kEpochs : 0; e < nep; ++e)
+                        mbar_wait_limit(bar(Plan::kBarXReady + e % Plan::kEpochs), static_cast<uint32_t>((e / Plan::kEpochs) & 1),
+                                        20ll * 1000 * 1000);
+                }
+            }
             const int lt = (wl / kULoadTeams) * 32 + lane;
             constexpr int LT = kULoadWarps / kULoadTeams * 32;
-            const float *xf = reinterpret_cast<const float *>(p.x);
-            for (int e = wl % kULoadTeams; e < nep; e += kULoadTeams) {
+            for (int e = wl % kULoadTeams; p.x_planes == nullptr && e < nep; e += kULoadTeams) {
                 if (wl == 0 && lane == 0) DMM_STAMP(3, e, 0);
                 if (e >= Plan::kEpochs)
                     mbar_wait(bar(Plan::kBarXFree + e % Plan::kEpochs), static_cast<uint32_t>(((e / Plan::kEpochs) - 1) & 1), flags);
@@ -758,26 +890,7 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
                             const int kt = gt - (gt / KT) * KT;
                             const long long k0 = 32ll * kt + 8 * kc;
                             dst[u] = ebuf + jl * tile_b + (kc >> 1) * (tile_b / 2) + row * 16 + (kc & 1) * 8;
-                            if (p.x_mode == kXHalf) {
-                                const uint4 v = __ldg(reinterpret_cast<const uint4 *>(x + row * p.x_ld + k0));
-                                h[u][0] = v.x; h[u][1] = v.y; h[u][2] = v.z; h[u][3] = v.w;
-                            } else {
-                                const float4 a0 = __ldcg(reinterpret_cast<const float4 *>(xf + row * p.x_ld + k0));
-                                const float4 a1 = __ldcg(reinterpret_cast<const float4 *>(xf + row * p.x_ld + k0 + 4));
-                                float f[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-                                if (p.x_mode == kXSiluMul) {
-                                    const float4 b0 = __ldcg(reinterpret_cast<const float4 *>(xf + row * p.x_ld + p.x_gap + k0));
-                                    const float4 b1 = __ldcg(reinterpret_cast<const float4 *>(xf + row * p.x_ld + p.x_gap + k0 + 4));
-                                    const float g[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
-#pragma unroll
-                                    for (int j = 0; j < 8; ++j) f[j] = __fdividef(f[j], 1.0f + __expf(-f[j])) * g[j];
-                                }
-#pragma unroll
-                                for (int j = 0; j < 4; ++j) {
-                                    const __half2 hh = __floats2half2_rn(f[2 * j], f[2 * j + 1]);
-                                    h[u][j] = *reinterpret_cast<const uint32_t *>(&hh);
-                                }
-                            }
+                            load_piece(p.x, p.x_mode, p.x_ld, p.x_gap, row, k0, h[u]);
                         }
                     }
 #pragma unroll
@@ -785,14 +898,8 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
                         if (dst[u] != 0) {
 #pragma unroll
                             for (int pl = 0; pl < 4; ++pl) {
-                                // plane pl = top byte of each half (an E5M2 number), then subtract it
-                                sts64(dst[u] + pl * (tile_b / 8), prmt(h[u][0], h[u][1], 0x7531u), prmt(h[u][2], h[u][3], 0x7531u));
-#pragma unroll
-                                for (int j = 0; j < 4; ++j) {
-                                    const uint32_t top = h[u][j] & 0xFF00FF00u;
-                                    __half2 rr = __hsub2(*reinterpret_cast<__half2 *>(&h[u][j]), *reinterpret_cast<const __half2 *>(&top));
-                                    h[u][j] = *reinterpret_cast<uint32_t *>(&rr);
-                                }
+                                const uint2 b8 = next_plane(h[u]);
+                                sts64(dst[u] + pl * (tile_b / 8), b8.x, b8.y);
                             }
                         }
                     }
@@ -916,9 +1023,35 @@ inline int launch_umma_one(const UmmaParams &p_in, int num_sms, bool pdl, cudaSt
     return cudaLaunchKernelEx(&cfg, kernel, p, map);
 }
 
-// f8 != 0: PolF8 (needs M <= 8); else PolF16 with M <= 64.
+// From this batch size on the fp8-operand path splits the activations into planes with
+// planes_kernel before the matmul kernel instead of inside it.
+constexpr long long kPlanesMinBatch = 4;
+
+// Padded batch rows of the plane layout for a batch of M (<= 32) rows.
+inline int planes_rows(long long M) { return M <= 8 ? static_cast<int>(M) : (M <= 16 ? 16 : 32); }
+
+inline int launch_planes(const void *x, int x_mode, long long x_ld, long long x_gap, int M, long long K, uint8_t *planes,
+                         bool pdl, cudaStream_t stream) {
+    const long long pieces = K / 16 * 2 * M;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>((pieces + 127) / 128));
+    cfg.blockDim = dim3(128);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, planes_kernel, x, x_mode, x_ld, x_gap, M, K, planes_rows(M), planes);
+}
+
+// f8 != 0: PolF8 (needs M <= 32); else PolF16 with M <= 64.
 inline int launch_umma(bool f8, const UmmaParams &p, int num_sms, bool pdl, cudaStream_t stream) {
-    if (f8) return launch_umma_one<PolF8, 32>(p, num_sms, pdl, stream);
+    if (f8) {
+        if (p.M <= 8) return launch_umma_one<PolF8, 32>(p, num_sms, pdl, stream);
+        if (p.M <= 16) return launch_umma_one<PolF8, 64>(p, num_sms, pdl, stream);
+        return launch_umma_one<PolF8, 128>(p, num_sms, pdl, stream);
+    }
     if (p.M <= 16) return launch_umma_one<PolF16, 16>(p, num_sms, pdl, stream);
     if (p.M <= 32) return launch_umma_one<PolF16, 32>(p, num_sms, pdl, stream);
     return launch_umma_one<PolF16, 64>(p, num_sms, pdl, stream);
@@ -926,7 +1059,7 @@ inline int launch_umma(bool f8, const UmmaParams &p, int num_sms, bool pdl, cuda
 
 // Workspace floats per CTA slot for a batch of M columns on this path.
 inline int umma_partial_values(long long M, bool f8) {
-    const int nb = f8 ? 8 : (M <= 16 ? 16 : (M <= 32 ? 32 : 64));
+    const int nb = f8 ? (M <= 8 ? 8 : (M <= 16 ? 16 : 32)) : (M <= 16 ? 16 : (M <= 32 ? 32 : 64));
     return 2 * nb * 128;
 }
 

@@ -100,12 +100,12 @@ class LinearStack:
     def step(self, h: torch.Tensor, path: int = _lib.PATH_AUTO, fused: bool | None = None) -> torch.Tensor:
         """One pass of the stack over the fp32 residual stream ``h`` [B, hidden] (updated in place).
 
-        ``fused`` (default: whenever the batch is at most 8): every elementwise step between two
+        ``fused`` (default: whenever the batch is at most 32): every elementwise step between two
         layers runs inside the matmul kernels -- the loaders read fp32 and round to fp16 or form
         silu(gate) * up, the epilogues add onto the residual stream with atomic adds, and each
         kernel clears the buffer a later kernel accumulates into.  Four launches per block."""
         if fused is None:
-            fused = h.shape[0] <= 8 and path == _lib.PATH_AUTO
+            fused = h.shape[0] <= 32 and path == _lib.PATH_AUTO
         if fused:
             return self._step_fused(h)
         hid_loc = self.hidden // self.world

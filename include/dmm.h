@@ -51,8 +51,8 @@ extern "C" {
 #define DMM_PATH_AUTO 0
 #define DMM_PATH_GEMV 1       /* streaming kernel on warp-level MMAs, any M */
 #define DMM_PATH_TCGEN05 2    /* tcgen05 + TMEM, decoded weights as fp16 operands, any M */
-#define DMM_PATH_TCGEN05_F8 3 /* tcgen05 + TMEM, weights as fp6 and activations as exact fp8 planes;
-                                 the small-batch path, taken per chunk of 8 batch columns */
+#define DMM_PATH_TCGEN05_F8 3 /* tcgen05 + TMEM, weights as fp6 and activations as exact fp8 planes,
+                                 32 batch rows per pass over the weights; what DMM_PATH_AUTO takes */
 
 /* what dmm_f16_fused reads as activations */
 #define DMM_X_F16 0          /* fp16 [M, x_ld] */

@@ -117,7 +117,8 @@ def test_int_family_synthetic_codebook_and_extremes():
 
 
 F16_SHAPES = [(1, 16, 32), (1, 4096, 4096), (1, 11008, 4096), (1, 4096, 11008), (2, 48, 160), (4, 4096, 4096),
-              (8, 4096, 11008), (16, 1024, 2048), (1, 8192, 8192), (1, 10240, 8192), (33, 256, 512)]
+              (8, 4096, 11008), (16, 1024, 2048), (1, 8192, 8192), (1, 10240, 8192), (33, 256, 512),
+              (3, 2048, 1056), (9, 528, 2048), (24, 2048, 4096), (32, 4096, 2048)]
 
 
 def _check_f16(y, want):
@@ -161,14 +162,15 @@ def test_fp16_family_large_batch_and_accumulate(path):
     _check_f16(y.cpu().numpy(), base + o.decode_matmul_f16(x, codes, cb16, 0.125, o.SIGN_FAST))
 
 
-def test_fp8_plane_split_is_exact_for_awkward_activations():
+@pytest.mark.parametrize("M", [2, 4, 12, 20])  # split inside the kernel (M < 4) and by planes_kernel, all row paddings
+def test_fp8_plane_split_is_exact_for_awkward_activations(M):
     """Subnormal, tiny, huge and all-mantissa-bits halves: the four E5M2 planes must add up exactly."""
     rng = np.random.default_rng(9)
-    M, N, K = 4, 256, 512
+    N, K = 256, 512
     cb16 = o.synthetic_codebook(42)
     bits = rng.integers(0, 0x7C00, size=(M, K)).astype(np.uint16)  # every finite positive half pattern
     bits[1] |= 0x8000
-    bits[2, ::2] = rng.integers(0, 0x0400, size=K // 2).astype(np.uint16)  # subnormals
+    bits[M - 1, ::2] = rng.integers(0, 0x0400, size=K // 2).astype(np.uint16)  # subnormals
     x = (bits.view(np.float16).astype(np.float32) * np.float32(2.0 ** -10)).astype(np.float16)
     codes = _codes(rng, N, K)
     want = o.decode_matmul_f16(x, codes, cb16, 1.0)
@@ -306,3 +308,20 @@ def test_linear_stack_fused_step_matches_unfused():
     one = LinearStack(dict(cfg, layers=1), cb16, "cuda", seed=5, scale=2.0 ** -8)
     got = one.step(h0.clone(), fused=True).cpu().numpy()
     assert np.abs(got - h).max() <= 2e-3
+
+
+@pytest.mark.parametrize("batch", [5, 16, 32])
+def test_linear_stack_fused_step_at_larger_batches(batch):
+    """From 4 batch rows on the fused step splits the activations with planes_kernel (fp32 and
+    SiLU inputs included) and switches to the 64- and 128-column MMA variants: same result as the
+    plain step."""
+    from decode_matmul_b200.linear import LinearStack
+
+    cfg = dict(hidden=512, kv_heads=2, head_dim=64, ffn=1024, layers=2)
+    stack = LinearStack(cfg, dmm.synthetic_codebook(42), "cuda", seed=6, scale=2.0 ** -8)
+    torch.manual_seed(batch)
+    h0 = torch.randn(batch, 512, device="cuda")
+    h_fused = stack.step(h0.clone(), fused=True)
+    h_plain = stack.step(h0.clone(), fused=False)
+    assert dmm.status() == 0
+    assert torch.allclose(h_fused, h_plain, rtol=2e-3, atol=2e-3)

@@ -227,12 +227,9 @@ struct UmmaPlan {
     static constexpr uint32_t kXStage = Pol::kG * Pol::x_tile_bytes(NMMA);
     // fp8 policy: the activation planes of a whole run of k-tiles ("epoch") stay resident in one
     // of kEpochs buffers, densely packed [tile][k-half][plane][row < M][16 B]
-    // (128 columns = 32 batch rows: a k-tile of planes is 4 KiB, so more and smaller buffers)
-#ifndef DMM_EPOCHS128
-#define DMM_EPOCHS128 7
-#endif
-    static constexpr int kEpochs = NMMA > 64 ? DMM_EPOCHS128 : 4;
-    static constexpr uint32_t kEpochBytes = NMMA > 64 ? 8192 : 14336;
+    // (128 columns = 32 batch rows: a k-tile of planes is 4 KiB; an epoch is then one chunk)
+    static constexpr int kEpochs = NMMA > 64 ? 3 : 4;
+    static constexpr uint32_t kEpochBytes = NMMA > 64 ? 16384 : 14336;
     static constexpr uint32_t kXBytes = Pol::kIsF8 ? kEpochs * kEpochBytes + 256 : kSlots * kXStage;
     static constexpr int kNB = Pol::out_cols(NMMA);               // output columns per launch
     static constexpr uint32_t kPreBytes = kUBarBytes + kXBytes;
@@ -693,8 +690,11 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
             const uint64_t xdesc0 = Pol::kIsF8 ? smem_desc(x_addr, tile_b / 2, NMMA > 32 ? 128u : tile_b / 8)
                                                : smem_desc(x_addr, NMMA * 16, 128);
             int cur_ep = -1, ep_beg = 0, ep_end = 0;  // fp8: epoch being read and its k-tile range
-            uint32_t ep_addr = 0;
+            int ep_slot = 0;                          // its buffer, the parity of that buffer's barriers
+            uint32_t ep_par = 0, ep_addr = 0;
             const uint32_t xdesc_lo = static_cast<uint32_t>(xdesc0), xdesc_hi = static_cast<uint32_t>(xdesc0 >> 32);
+            // accumulator of the (first) MMA tile this warp issues
+            const uint32_t d_col0 = tmem + static_cast<uint32_t>(((TP == 2 ? tp : 0) * NACC + me) * NMMA);
             int cbase = 0, jseg = 0;  // chunks / k-tiles of earlier segments
             for (int ss = ss_first; ss <= ss_last; cbase += seg_chunks(ss), jseg += seg_len(ss), ++ss, ++segidx) {
                 const int len = seg_len(ss);
@@ -707,9 +707,9 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
                 for (int c = (me - cbase) & (NACC - 1); c < nchunks; c += NACC) {
                     const int q = (cbase + c) & 3;
                     const int n = len - c * C < C ? len - c * C : C;
+                    uint32_t cn = q == 0 ? cnt0 : q == 1 ? cnt1 : q == 2 ? cnt2 : cnt3;  // groups taken from group q so far
 #pragma unroll 1
-                    for (int g0 = 0; g0 < n; g0 += G) {
-                        const uint32_t cn = q == 0 ? cnt0 : q == 1 ? cnt1 : q == 2 ? cnt2 : cnt3;
+                    for (int g0 = 0; g0 < n; g0 += G, ++cn) {
                         const int sl = q * NA + static_cast<int>(cn % NA);
                         if (wi == 0 && leader) DMM_STAMP(2, cn * 2 + (q >> 1), 0);
                         const uint32_t a_col = tmem + Plan::kDCols + static_cast<uint32_t>(sl) * Plan::kBufCols;
@@ -724,24 +724,34 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
                                 if (g0 + i < n) {
                                     const int jt = jseg + c * C + g0 + i;  // CTA-wide k-tile index
                                     if (jt >= ep_end) {
-                                        // step to the epoch that holds jt (no division: an issuer only moves forward)
-                                        int e = cur_ep < 0 ? 0 : cur_ep;
-                                        while (jt >= E0 + e * E) {
-                                            if (leader) tc_commit(bar(Plan::kBarXFree + e % Plan::kEpochs));  // also epochs it never read
-                                            ++e;
-                                        }
-                                        mbar_wait(bar(Plan::kBarXReady + e % Plan::kEpochs), static_cast<uint32_t>((e / Plan::kEpochs) & 1), flags);
-                                        cur_ep = e;
-                                        ep_beg = e == 0 ? 0 : E0 + (e - 1) * E;
-                                        ep_end = E0 + e * E;
-                                        ep_addr = ((e % Plan::kEpochs) * Plan::kEpochBytes) >> 4;
+                                        // step to the epoch that holds jt, releasing the ones left behind
+                                        // (also epochs this issuer never read: every issuer arrives on
+                                        // every epoch).  All state moves incrementally: no division, no
+                                        // modulo in a loop that one thread runs between two MMAs.
+                                        do {
+                                            if (cur_ep >= 0) {
+                                                if (leader) tc_commit(bar(Plan::kBarXFree + ep_slot));
+                                                if (++ep_slot == Plan::kEpochs) {
+                                                    ep_slot = 0;
+                                                    ep_par ^= 1u;
+                                                }
+                                            }
+                                            ++cur_ep;
+                                            ep_beg = ep_end;
+                                            ep_end += cur_ep == 0 ? E0 : E;
+                                        } while (jt >= ep_end);
+                                        mbar_wait(bar(Plan::kBarXReady + ep_slot), ep_par, flags);
+                                        ep_addr = (static_cast<uint32_t>(ep_slot) * Plan::kEpochBytes) >> 4;
                                     }
                                     const uint32_t xlo = xdesc_lo + ep_addr + ((static_cast<uint32_t>(jt - ep_beg) * tile_b) >> 4);
                                     const uint32_t acc = (first && i == 0) ? 0u : 1u;
                                     if (leader) {
-                                        for (int t = t_lo; t < t_hi; ++t)
-                                            mma_ts_f8_lh(tmem + static_cast<uint32_t>((t * NACC + me) * NMMA),
-                                                         a_col + (t * G + i) * Pol::kACols, xlo, xdesc_hi, idesc, acc);
+                                        if constexpr (TP == 1) {
+                                            mma_ts_f8_lh(d_col0, a_col + i * Pol::kACols, xlo, xdesc_hi, idesc, acc);
+                                            mma_ts_f8_lh(d_col0 + NACC * NMMA, a_col + (G + i) * Pol::kACols, xlo, xdesc_hi, idesc, acc);
+                                        } else {
+                                            mma_ts_f8_lh(d_col0, a_col + (tp * G + i) * Pol::kACols, xlo, xdesc_hi, idesc, acc);
+                                        }
                                     }
                                 }
                             }
@@ -761,8 +771,8 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
                         first = false;
                         if (leader) tc_commit(bar(Plan::kBarFree + sl));
                         if (wi == 0 && leader) DMM_STAMP(2, cn * 2 + (q >> 1), 2);
-                        if (q == 0) ++cnt0; else if (q == 1) ++cnt1; else if (q == 2) ++cnt2; else ++cnt3;
                     }
+                    if (q == 0) cnt0 = cn; else if (q == 1) cnt1 = cn; else if (q == 2) cnt2 = cn; else cnt3 = cn;
                 }
                 if (leader) tc_commit(bar(Plan::kBarDReady));
             }
@@ -770,6 +780,7 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
                 const int nep = i1 - i0 <= E0 ? 1 : 1 + (i1 - i0 - E0 + E - 1) / E;
                 for (int r = cur_ep < 0 ? 0 : cur_ep; r < nep; ++r)
                     if (leader) tc_commit(bar(Plan::kBarXFree + r % Plan::kEpochs));
+                (void)ep_slot;
             }
         }
     } else if (warp == kUTmaWarp) {

@@ -18,6 +18,8 @@ struct DeviceState {
     int num_sms = 0;
     void *workspace = nullptr;  // library-owned default workspace
     size_t workspace_bytes = 0;
+    void *retile = nullptr;     // library-owned buffer for codes re-tiled from the fast layout
+    size_t retile_bytes = 0;
 };
 
 static std::mutex g_mutex;
@@ -89,6 +91,33 @@ static int resolve_workspace(DeviceState *d, long long M, long long N, long long
     }
     (void)stream;
     *ws = d->workspace;
+    return 0;
+}
+
+// Codes given in the fast layout are re-tiled into a library-owned buffer (grown on demand) and
+// the call goes on with the tile layout: one extra pass over the codes.  The reference's fast
+// kernel is an unbuilt prototype; this keeps its entry point usable, not fast.
+static int retile_fast(DeviceState *d, const void *codes, long long N, long long K, cudaStream_t stream,
+                       const void **tiled) {
+    if (N % 32 != 0) return DMM_ERR_SHAPE;
+    const size_t need = static_cast<size_t>(N) * static_cast<size_t>(K) / 4;
+    {
+        std::lock_guard<std::mutex> lock(g_mutex);
+        if (d->retile_bytes < need) {
+            cudaError_t err = cudaDeviceSynchronize();  // earlier calls may still read the old buffer
+            if (err != cudaSuccess) return err;
+            if (d->retile) cudaFree(d->retile);
+            d->retile = nullptr;
+            d->retile_bytes = 0;
+            err = cudaMalloc(&d->retile, need);
+            if (err != cudaSuccess) return err;
+            d->retile_bytes = need;
+        }
+    }
+    const int rc = launch_retile_fast(codes, d->retile, N, K, stream);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    if (rc) return rc;
+    *tiled = d->retile;
     return 0;
 }
 
@@ -239,8 +268,15 @@ int dmm_i8(const int8_t *x, const int16_t *codes, const int64_t *cb64, int32_t *
            int sign_convention, int layout, unsigned flags, void *workspace, size_t workspace_bytes, void *stream) {
     int rc = check_common(x, codes, cb64, out, M, N, K, sign_convention, layout);
     if (rc) return rc;
-    if (layout != DMM_LAYOUT_TILE) return DMM_ERR_UNSUPPORTED;
-    return run_stream(0, x, codes, cb64, 0, 1.0f, out, M, N, K, sign_convention, flags, workspace, workspace_bytes,
+    const void *tiled = codes;
+    if (layout == DMM_LAYOUT_FAST) {
+        DeviceState *d = nullptr;
+        rc = current_device_state(&d);
+        if (rc) return rc;
+        rc = retile_fast(d, codes, N, K, static_cast<cudaStream_t>(stream), &tiled);
+        if (rc) return rc;
+    }
+    return run_stream(0, x, tiled, cb64, 0, 1.0f, out, M, N, K, sign_convention, flags, workspace, workspace_bytes,
                       static_cast<cudaStream_t>(stream));
 }
 
@@ -255,8 +291,16 @@ int dmm_f16_fused(const void *x, int x_kind, int64_t x_ld, int64_t x_gap, const 
     if (x_kind != DMM_X_F16 && x_kind != DMM_X_F32 && x_kind != DMM_X_F32_SILU_MUL) return DMM_ERR_ARG;
     if (x_ld < K || x_ld % 8 != 0 || x_gap % 4 != 0 || (x_kind == DMM_X_F32_SILU_MUL && x_gap + K > x_ld))
         return DMM_ERR_SHAPE;
-    if (layout != DMM_LAYOUT_TILE) return DMM_ERR_UNSUPPORTED;
     if (zero_count < 0 || (zero_count > 0 && zero_ptr == nullptr)) return DMM_ERR_ARG;
+    if (layout == DMM_LAYOUT_FAST) {
+        DeviceState *d = nullptr;
+        rc = current_device_state(&d);
+        if (rc) return rc;
+        const void *tiled = nullptr;
+        rc = retile_fast(d, codes, N, K, static_cast<cudaStream_t>(stream), &tiled);
+        if (rc) return rc;
+        codes = reinterpret_cast<const int16_t *>(tiled);
+    }
     if (path == DMM_PATH_AUTO) path = x_kind == DMM_X_F16 ? dmm_select_path(M, N, K) : DMM_PATH_TCGEN05_F8;
     if (zero_count > 0 && path != DMM_PATH_TCGEN05 && path != DMM_PATH_TCGEN05_F8) return DMM_ERR_UNSUPPORTED;
     // fp32 inputs are converted by the loaders of the fp8-operand kernel only
@@ -323,10 +367,15 @@ int dmm_decode(const int16_t *codes, const void *cb, int cb_is_f16, void *W_out,
     if (sign_convention != DMM_SIGN_SLOW && sign_convention != DMM_SIGN_FAST) return DMM_ERR_ARG;
     if (layout != DMM_LAYOUT_TILE && layout != DMM_LAYOUT_FAST) return DMM_ERR_ARG;
     if (!aligned16(codes) || !aligned16(cb) || !aligned16(W_out)) return DMM_ERR_ALIGN;
-    if (layout != DMM_LAYOUT_TILE) return DMM_ERR_UNSUPPORTED;
     DeviceState *d = nullptr;
     int rc = current_device_state(&d);
     if (rc) return rc;
+    if (layout == DMM_LAYOUT_FAST) {
+        const void *tiled = nullptr;
+        rc = retile_fast(d, codes, N, K, static_cast<cudaStream_t>(stream), &tiled);
+        if (rc) return rc;
+        codes = reinterpret_cast<const int16_t *>(tiled);
+    }
     rc = launch_decode(codes, cb, cb_is_f16 ? 1 : 0, W_out, N, K, sign_convention, d->num_sms,
                        static_cast<cudaStream_t>(stream));
     g_launches.fetch_add(1, std::memory_order_relaxed);

@@ -9,6 +9,46 @@ namespace dmm {
 
 constexpr int kDecodeThreads = 512;
 
+// Re-tiles codes from the layout of fast_decode_matmul_cuda -- flat uint32 [N/32][K/16][lane:32],
+// word = code(n = 32*nb + lane, j = 2*kp) | code(j = 2*kp + 1) << 16, the completion this build
+// defines for the reference's lane-per-column reads (fast_decode_matmul_cuda.cu:106,110-113,130) --
+// into the tile layout [N/16][K/32][g:8][t:4][h:2] that every kernel of this library streams.
+// One warp per (32-row block, k-tile): 256 contiguous bytes in, 256 contiguous bytes out; lane l
+// holds the four codes of row 32*nb + l and trades two of them with lane l ^ 8 (rows g and g + 8
+// of a strip share a 32-bit word of the tile layout).
+__global__ void __launch_bounds__(256) retile_fast_kernel(const uint32_t *__restrict__ fast, uint32_t *__restrict__ tiled,
+                                                          long long N, long long K) {
+    const long long KT = K / 32;
+    const long long warp = (blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x) >> 5;
+    const int lane = threadIdx.x & 31;
+    if (warp >= (N / 32) * KT) return;
+    const long long nb = warp / KT, kt = warp - nb * KT;
+    const uint32_t *src = fast + (nb * (K / 16) + 2 * kt) * 32;
+    const uint32_t w0 = __ldg(src + lane), w1 = __ldg(src + 32 + lane);  // codes j = 4kt, 4kt+1 | 4kt+2, 4kt+3
+    const uint32_t p0 = __shfl_xor_sync(0xffffffffu, w0, 8), p1 = __shfl_xor_sync(0xffffffffu, w1, 8);
+    const int strip = lane >> 4, h = (lane >> 3) & 1, g = lane & 7;
+    // word (g, t) of the tile layout = code of row g (low half) | code of row g + 8 (high half)
+    uint2 out;
+    if (h == 0) {  // this lane is row g: writes t = 0, 1 from its w0 and the partner's w0
+        out.x = (w0 & 0xFFFFu) | (p0 << 16);
+        out.y = (w0 >> 16) | (p0 & 0xFFFF0000u);
+    } else {       // this lane is row g + 8: writes t = 2, 3 from the partner's w1 and its own
+        out.x = (p1 & 0xFFFFu) | (w1 << 16);
+        out.y = (p1 >> 16) | (w1 & 0xFFFF0000u);
+    }
+    uint32_t *dst = tiled + ((2 * nb + strip) * KT + kt) * 32 + g * 4 + h * 2;
+    *reinterpret_cast<uint2 *>(dst) = out;
+}
+
+inline int launch_retile_fast(const void *fast, void *tiled, long long N, long long K, cudaStream_t stream) {
+    const long long warps = (N / 32) * (K / 32);
+    const unsigned blocks = static_cast<unsigned>((warps + 7) / 8);
+    retile_fast_kernel<<<blocks, 256, 0, stream>>>(reinterpret_cast<const uint32_t *>(fast),
+                                                   reinterpret_cast<uint32_t *>(tiled), N, K);
+    return cudaGetLastError();
+}
+
+
 // One thread per 32-bit word of the tile layout (two codes: strip rows g and g+8).
 template <bool kF16>
 __global__ void __launch_bounds__(kDecodeThreads) decode_kernel(const uint32_t *__restrict__ words,

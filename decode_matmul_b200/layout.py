@@ -26,6 +26,26 @@ def untranspose_tile(tiled: torch.Tensor) -> torch.Tensor:
     return t.contiguous().reshape(n, k8)
 
 
+def fast_pack(codes: torch.Tensor) -> torch.Tensor:
+    """Logical int16 [N, K/8] -> the layout of ``fast_decode_matmul_cuda``: flat uint32 order
+    [N/32][K/16][lane:32], word = code(n = 32*nb + lane, j = 2*kp) | code(j = 2*kp + 1) << 16.
+    The reference's fast kernel reads one such word per lane, a warp covering 32 consecutive
+    output columns (fast_decode_matmul_cuda.cu:106,110-113,130); its k addressing is not
+    self-consistent, so this build defines the completion.  Shape stays [N, K/8]."""
+    n, k8 = codes.shape
+    if n % 32 or k8 % 4:
+        raise RuntimeError("fast_pack: need N % 32 == 0 and K % 32 == 0")
+    t = codes.reshape(n // 32, 32, k8 // 2, 2).permute(0, 2, 1, 3)
+    return t.contiguous().reshape(n, k8)
+
+
+def fast_unpack(packed: torch.Tensor) -> torch.Tensor:
+    """Inverse of :func:`fast_pack`."""
+    n, k8 = packed.shape
+    t = packed.reshape(n // 32, k8 // 2, 32, 2).permute(0, 2, 1, 3)
+    return t.contiguous().reshape(n, k8)
+
+
 def shard_rows(codes: torch.Tensor, world: int, rank: int) -> torch.Tensor:
     """Column-parallel shard (split N) of a LOGICAL code matrix."""
     n = codes.shape[0]

@@ -12,6 +12,16 @@
  *   codes_tiled    int16, N*K/8 values in the tile layout of the reference's
  *                  transpose_tile() (test_decode_matmul.py:101-109):
  *                  [N/16][K/32][g:8][t:4][h:2], row n = 16*nt + 8*h + g, column j = 4*kt + t.
+ *   codes_fast     the layout of fast_decode_matmul_cuda (DMM_LAYOUT_FAST): flat uint32
+ *                  [N/32][K/16][lane:32], word = code(n = 32*nb + lane, j = 2*kp) |
+ *                  code(j = 2*kp + 1) << 16 -- one word per lane, a warp covering 32 consecutive
+ *                  output columns, as the reference's fast kernel reads them
+ *                  (fast_decode_matmul_cuda.cu:106,110-113,130); that kernel's k addressing is
+ *                  not self-consistent, so the k order is this library's completion of it.
+ *                  Needs N % 32 == 0.  Every entry point accepts it: the codes are re-tiled into
+ *                  a library-owned device buffer first (one extra pass over the codes, and a
+ *                  cudaMalloc when the buffer has to grow), then the call proceeds as for the
+ *                  tile layout.
  *   cb64           int64[256]; byte i of entry e is int8(4 * codebook value i)
  *                  (test_decode_matmul.py:85).
  *   cb16           fp16[256][8]; the same table as real values (byte / 4).

@@ -325,3 +325,29 @@ def test_linear_stack_fused_step_at_larger_batches(batch):
     h_plain = stack.step(h0.clone(), fused=False)
     assert dmm.status() == 0
     assert torch.allclose(h_fused, h_plain, rtol=2e-3, atol=2e-3)
+
+
+@pytest.mark.parametrize("M,N,K", [(8, 64, 512), (1, 4096, 4096), (13, 1056 - 32, 1056)])
+def test_fast_entry_point_and_layout(M, N, K, e8p):
+    """fast_decode_matmul_cuda.decode_matmul: fast layout, that file's sign convention (parity ->
+    weight 0), accumulation into the caller's output -- exact against the oracle."""
+    import fast_decode_matmul_cuda as fast
+
+    rng = np.random.default_rng(M + N + K)
+    x = rng.integers(-128, 128, size=(M, K)).astype(np.int8)
+    codes = _codes(rng, N, K)
+    base = rng.integers(-1000, 1000, size=(M, N)).astype(np.int32)
+    out = _dev(base)
+    got = fast.decode_matmul(_dev(x), _dev(o.fast_pack(codes)), _dev(e8p), out)
+    assert got.data_ptr() == out.data_ptr()
+    want = base + o.decode_matmul_int(x, codes, e8p, o.SIGN_FAST)
+    assert np.array_equal(got.cpu().numpy(), want)
+    # the same layout through the fp16 family and the decode-only export
+    cb16 = o.cb64_to_cb16(e8p)
+    x16 = rng.standard_normal((M, K)).astype(np.float16)
+    y = dmm.decode_matmul_fp16(_dev(x16), _dev(o.fast_pack(codes)), _dev(cb16), 1.0,
+                               layout=dmm.LAYOUT_FAST, sign_convention=dmm.SIGN_FAST)
+    _check_f16(y.cpu().numpy(), o.decode_matmul_f16(x16, codes, cb16, 1.0, o.SIGN_FAST))
+    w = dmm.decode_weights(_dev(o.fast_pack(codes)), _dev(e8p), layout=dmm.LAYOUT_FAST, sign_convention=dmm.SIGN_FAST)
+    assert np.array_equal(w.cpu().numpy(), o.decode_weights(codes, e8p, o.SIGN_FAST))
+    assert dmm.status() == 0

@@ -99,3 +99,20 @@ def test_shards_tile_independently():
         assert torch.equal(dmm.transpose_tile(rows[r]).reshape(-1), whole[r * whole.numel() // 2:(r + 1) * whole.numel() // 2])
     cols = [dmm.shard_cols(codes, 2, r) for r in range(2)]
     assert torch.equal(torch.cat(cols, 1), codes)
+
+
+def test_fast_layout_packers_match_oracle():
+    import numpy as np
+    import torch
+
+    from decode_matmul_b200 import layout
+    from oracle import dmm_oracle as o
+
+    rng = np.random.default_rng(4)
+    codes = rng.integers(-32768, 32768, size=(96, 40)).astype(np.int16)
+    t = torch.from_numpy(codes)
+    packed = layout.fast_pack(t)
+    assert np.array_equal(packed.numpy(), o.fast_pack(codes))
+    assert torch.equal(layout.fast_unpack(packed), t)
+    with pytest.raises(RuntimeError):
+        layout.fast_pack(t[:48])  # N % 32

@@ -17,9 +17,19 @@ X_F16, X_F32, X_F32_SILU_MUL = 0, 1, 2
 STATUS_WAIT_TIMEOUT, STATUS_BAD_CODEBOOK, STATUS_BAD_SMEM = 1, 2, 4
 
 EXPORTS = (
-    "dmm_i8", "dmm_f16", "dmm_f16_fused", "dmm_f16_noalloc", "dmm_decode", "dmm_workspace_bytes", "dmm_status", "dmm_select_path",
+    "dmm_i8", "dmm_f16", "dmm_f16_fused", "dmm_f16_chain", "dmm_f16_noalloc", "dmm_decode", "dmm_workspace_bytes", "dmm_status", "dmm_select_path",
     "dmm_launch_count", "dmm_error_string", "dmm_version",
 )
+
+
+CHAIN_MAX_OPS = 8
+
+
+class ChainOp(ctypes.Structure):
+    """``dmm_chain_op`` of include/dmm.h."""
+    _fields_ = [("x", ctypes.c_void_p), ("x_kind", ctypes.c_int), ("x_ld", ctypes.c_int64), ("x_gap", ctypes.c_int64),
+                ("codes", ctypes.c_void_p), ("scale", ctypes.c_float), ("out", ctypes.c_void_p), ("N", ctypes.c_int64),
+                ("K", ctypes.c_int64), ("zero_ptr", ctypes.c_void_p), ("zero_count", ctypes.c_int64)]
 
 
 def lib() -> ctypes.CDLL:
@@ -43,6 +53,8 @@ def lib() -> ctypes.CDLL:
     L.dmm_f16_fused.argtypes = [vp, ci, i64, i64, vp, vp, ctypes.c_float, vp, i64, i64, i64, ci, ci, ci, cu, vp, i64, vp, sz,
                                 vp]
     L.dmm_f16_fused.restype = ci
+    L.dmm_f16_chain.argtypes = [vp, ci, vp, i64, ci, cu, vp]
+    L.dmm_f16_chain.restype = ci
     L.dmm_f16_noalloc.argtypes = [vp, vp, vp, ctypes.c_float, vp, i64, i64, i64, ci, cu, vp]
     L.dmm_f16_noalloc.restype = ci
     L.dmm_decode.argtypes = [vp, vp, ci, vp, i64, i64, ci, ci, vp]

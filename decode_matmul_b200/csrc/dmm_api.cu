@@ -20,6 +20,7 @@ struct DeviceState {
     size_t workspace_bytes = 0;
     void *retile = nullptr;     // library-owned buffer for codes re-tiled from the fast layout
     size_t retile_bytes = 0;
+    unsigned *chain_sync = nullptr;  // arrival counters of dmm_f16_chain (zero between launches)
 };
 
 static std::mutex g_mutex;
@@ -322,6 +323,59 @@ int dmm_f16(const void *x, const int16_t *codes, const void *cb16, float scale, 
                          nullptr, 0, workspace, workspace_bytes, stream);
 }
 
+int dmm_f16_chain(const dmm_chain_op *ops, int n_ops, const void *cb16, int64_t M, int sign_convention,
+                  unsigned flags, void *stream) {
+    if (!ops || !cb16) return DMM_ERR_NULL;
+    if (n_ops < 2 || n_ops > DMM_CHAIN_MAX_OPS) return DMM_ERR_ARG;
+    if (M < 1 || M > 8) return DMM_ERR_LIMIT;
+    if (flags & ~DMM_FLAG_PDL) return DMM_ERR_ARG;
+    DeviceState *d = nullptr;
+    int rc = current_device_state(&d);
+    if (rc) return rc;
+    {
+        std::lock_guard<std::mutex> lock(g_mutex);
+        if (d->chain_sync == nullptr) {
+            cudaError_t err = cudaMalloc(reinterpret_cast<void **>(&d->chain_sync), 256);
+            if (err != cudaSuccess) return err;
+            err = cudaMemset(d->chain_sync, 0, 256);
+            if (err != cudaSuccess) return err;
+        }
+    }
+    UmmaParams p[DMM_CHAIN_MAX_OPS] = {};
+    for (int i = 0; i < n_ops; ++i) {
+        const dmm_chain_op &o = ops[i];
+        rc = check_common(o.x, o.codes, cb16, o.out, M, o.N, o.K, sign_convention, DMM_LAYOUT_TILE);
+        if (rc) return rc;
+        if (o.x_kind != DMM_X_F16 && o.x_kind != DMM_X_F32 && o.x_kind != DMM_X_F32_SILU_MUL) return DMM_ERR_ARG;
+        if (o.x_ld < o.K || o.x_ld % 8 != 0 || o.x_gap % 4 != 0 || (o.x_kind == DMM_X_F32_SILU_MUL && o.x_gap + o.K > o.x_ld))
+            return DMM_ERR_SHAPE;
+        if (o.zero_count < 0 || (o.zero_count > 0 && o.zero_ptr == nullptr)) return DMM_ERR_ARG;
+        p[i].x = o.x;
+        p[i].x_mode = o.x_kind;
+        p[i].x_ld = o.x_ld;
+        p[i].x_gap = o.x_gap;
+        p[i].codes = o.codes;
+        p[i].cb = cb16;
+        p[i].out = o.out;
+        p[i].M = M;
+        p[i].N = o.N;
+        p[i].K = o.K;
+        p[i].scale = 2.0f * o.scale;  // accumulators hold sum(x * q / 8), weight = q / 4
+        p[i].accumulate = 1;
+        p[i].atomic_reduce = 1;
+        p[i].sign_convention = sign_convention;
+        p[i].zero_ptr = o.zero_ptr;
+        p[i].zero_count = o.zero_count;
+#ifdef DMM_TRACE
+        p[i].trace = g_trace;
+#endif
+    }
+    rc = launch_umma_chain(p, n_ops, d->chain_sync, d->num_sms, (flags & DMM_FLAG_PDL) != 0,
+                           static_cast<cudaStream_t>(stream));
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return rc;
+}
+
 int dmm_f16_noalloc(const void *x, const int16_t *codes, const void *cb16, float scale, float *out, int64_t M,
                     int64_t N, int64_t K, int sign_convention, unsigned flags, void *stream) {
     int rc = check_common(x, codes, cb16, out, M, N, K, sign_convention, DMM_LAYOUT_TILE);
@@ -401,6 +455,14 @@ int dmm_status(unsigned *status_out) {
     const unsigned zero = 0;
     err = cudaMemcpyToSymbol(g_status, &zero, sizeof(zero));
     if (err != cudaSuccess) return err;
+    if (v != 0) {
+        // a chain that gave up may have left its arrival counters behind
+        DeviceState *d = nullptr;
+        if (current_device_state(&d) == 0 && d->chain_sync != nullptr) {
+            err = cudaMemset(d->chain_sync, 0, 256);
+            if (err != cudaSuccess) return err;
+        }
+    }
     *status_out = v;
     return 0;
 }

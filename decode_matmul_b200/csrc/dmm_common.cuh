@@ -101,6 +101,26 @@ __device__ __forceinline__ void mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
 }
 
+// Waits (bounded, like mbar_wait) until a counter in global memory that other CTAs of the same
+// grid increment has reached `target`.  Only legal when all those CTAs are resident together.
+__device__ __forceinline__ void grid_wait(const unsigned *counter, unsigned target, volatile int *failed) {
+    if (*failed) return;
+    const long long t0 = clock64();
+    for (;;) {
+        unsigned v;
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(counter) : "memory");
+        if (v >= target) return;
+        if (clock64() - t0 > kWaitLimitCycles || *failed) {
+            if (!*failed) {
+                *failed = 1;
+                raise_status(DMM_STATUS_WAIT_TIMEOUT);
+            }
+            return;
+        }
+        __nanosleep(40);
+    }
+}
+
 // A plain bounded wait that ignores the CTA's failed flag: used on the way out of a kernel whose
 // earlier wait gave up, to let copies that are still in flight land.
 __device__ __forceinline__ void mbar_wait_limit(uint32_t bar, uint32_t parity, long long cycles) {

@@ -249,7 +249,8 @@ struct UmmaPlan {
     static constexpr int kBarXFree = kBarXReady + kEpochs;               // [kEpochs] both issuers (commit)
     static constexpr int kBarDReady = kBarXFree + kEpochs;
     static constexpr int kBarDFree = kBarDReady + 1;
-    static constexpr int kBarCount = kBarDFree + 1;
+    static constexpr int kBarGridOk = kBarDFree + 1;  // chains: this CTA's loaders have seen the previous op complete
+    static constexpr int kBarCount = kBarGridOk + 1;
     static_assert(kBarCount * 8 + 64 <= kUBarBytes, "barrier block too small");
 };
 
@@ -282,10 +283,22 @@ struct UmmaParams {
     long long *trace;    // debugging aid (builds with -DDMM_TRACE only): clock stamps of CTA 0
 };
 
+// Several dependent products in one launch ("chain"): op k+1 reads what op k wrote.  The CTAs
+// stay resident; between two ops only the activation loaders wait (for every CTA to have
+// finished op k, counted in `sync`), while the decoders already work on the weights of op k+1.
+constexpr int kMaxOps = 8;
+template <int kOps>
+struct UmmaChainT {
+    UmmaParams op[kOps];
+    CUtensorMap map[kOps];
+    int n_ops;
+    unsigned *sync;  // [n_ops] arrival counters in global memory, zero between launches (chains only)
+};
+
 #ifdef DMM_TRACE
 #define DMM_STAMP(role, idx, what)                                                              \
     do {                                                                                        \
-        if (p.trace != nullptr && blockIdx.x == 0 && (idx) < 64) p.trace[((role)*64 + (idx)) * 4 + (what)] = clock64(); \
+        if (ch.op[0].trace != nullptr && blockIdx.x == 0 && (idx) < 64) ch.op[0].trace[((role)*64 + (idx)) * 4 + (what)] = clock64(); \
     } while (0)
 #else
 #define DMM_STAMP(role, idx, what) do { } while (0)
@@ -295,7 +308,8 @@ struct UmmaParams {
 __device__ __forceinline__ void load_piece(const void *xp, int x_mode, long long x_ld, long long x_gap, int row,
                                            long long k0, uint32_t (&h)[4]) {
     if (x_mode == kXHalf) {
-        const uint4 v = __ldg(reinterpret_cast<const uint4 *>(reinterpret_cast<const __half *>(xp) + row * x_ld + k0));
+        // (ld.cg: inside a chain the same buffer is rewritten between ops, L1 could hold a stale line)
+        const uint4 v = __ldcg(reinterpret_cast<const uint4 *>(reinterpret_cast<const __half *>(xp) + row * x_ld + k0));
         h[0] = v.x; h[1] = v.y; h[2] = v.z; h[3] = v.w;
         return;
     }
@@ -355,9 +369,10 @@ __global__ void __launch_bounds__(128) planes_kernel(const void *x, int x_mode, 
 
 // `codes_map` is a 2-D tensor map of the tiled code matrix: inner dimension = one strip
 // (K/32 k-tiles x 32 uint32), outer dimension = strips; box = kC k-tiles x 16 strips.
-template <class Pol, int NMMA>
-__global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
-                                                            const __grid_constant__ CUtensorMap codes_map) {
+// kChain == false is the plain single-product kernel: the op loops below run once with every
+// per-op value a compile-time-known kernel parameter.
+template <class Pol, int NMMA, bool kChain>
+__global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const __grid_constant__ UmmaChainT<kChain ? kMaxOps : 1> ch) {
     using Plan = UmmaPlan<Pol, NMMA>;
     constexpr int C = Pol::kC, G = Pol::kG, NA = Pol::kNA, RING = Pol::kRing, NACC = Plan::kNAcc, NB = Plan::kNB;
     constexpr int TP = Plan::kTileParts;
@@ -375,31 +390,36 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
     // keeps what derives from it (roles, descriptors, TMEM addresses) in uniform registers
     const int tid = threadIdx.x, warp = __shfl_sync(0xffffffffu, tid >> 5, 0), lane = tid & 31;
     if (tid == 0) DMM_STAMP(0, 0, 0);
-    const uint4 cb_pre = lut_prefetch(p.cb, tid);  // the codebook is static data: fetch it first
+    const UmmaParams &p0 = ch.op[0];  // codebook, sign convention, batch and input kind are common to all ops
+    const int n_ops = kChain ? ch.n_ops : 1;
+    const uint4 cb_pre = lut_prefetch(p0.cb, tid);  // the codebook is static data: fetch it first
 
-    if (ring_addr + Plan::kRingBytes > base + p.dyn_smem_bytes) {  // uniform over the grid
+    if (ring_addr + Plan::kRingBytes > base + p0.dyn_smem_bytes) {  // uniform over the grid
         if (tid == 0) raise_status(DMM_STATUS_BAD_SMEM);
         return;
     }
 
-    const int KT = static_cast<int>(p.K / 32);
     const int cta = blockIdx.x;
-    const int i0 = part32_begin(p.part, cta), i1 = part32_begin(p.part, cta + 1);  // this CTA's tiles
-    const int ss_first = i0 / KT, ss_last = (i1 - 1) / KT;
-    // segment ss of this CTA: first k-tile and number of k-tiles
-    auto seg_kt0 = [&](int ss) -> int {
-        const int a = ss * KT;
-        return i0 > a ? i0 - a : 0;
-    };
-    auto seg_len = [&](int ss) -> int {
-        const int a = ss * KT;
-        const int lo = i0 > a ? i0 : a, hi = i1 < a + KT ? i1 : a + KT;
-        return hi - lo;
-    };
-    auto seg_chunks = [&](int ss) -> int { return (seg_len(ss) + C - 1) / C; };
-    // Chunks are numbered through all segments of the CTA (cbase = chunks of earlier segments);
-    // chunk number mod 4 is the decoder group and mod 2 the issuer, so consecutive chunks always
-    // go to different groups, also across a segment boundary.
+    // Per-op geometry, set by every role at the top of its op loop: this CTA's tiles [i0, i1) of
+    // the op's (super-tile, k-tile) sequence and the segments (parts of a super-tile) they span.
+#define DMM_OP_GEOMETRY(P)                                                                          \
+    const int KT = static_cast<int>((P).K / 32);                                                   \
+    const int i0 = part32_begin((P).part, cta), i1 = part32_begin((P).part, cta + 1);              \
+    const int ss_first = i0 / KT, ss_last = i1 > i0 ? (i1 - 1) / KT : ss_first - 1;                \
+    auto seg_kt0 = [&](int ss) -> int {                                                            \
+        const int a = ss * KT;                                                                     \
+        return i0 > a ? i0 - a : 0;                                                                \
+    };                                                                                             \
+    auto seg_len = [&](int ss) -> int {                                                            \
+        const int a = ss * KT;                                                                     \
+        const int lo = i0 > a ? i0 : a, hi = i1 < a + KT ? i1 : a + KT;                            \
+        return hi - lo;                                                                            \
+    };                                                                                             \
+    auto seg_chunks = [&](int ss) -> int { return (seg_len(ss) + C - 1) / C; };                    \
+    (void)seg_kt0; (void)seg_chunks; (void)ss_last
+    // Chunks are numbered through all segments and ops of the CTA (cbase = chunks before);
+    // chunk number mod 4 is the decoder group and mod kNAcc the issuer, so consecutive chunks
+    // always go to different groups, also across a segment or op boundary.
 
     if (tid == 0) DMM_STAMP(0, 2, 0);
     // ---- set-up ----
@@ -411,7 +431,7 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
     bool bad_cb = false;
     if (warp < kUDecWarps) {
         if (tid == 0) DMM_STAMP(0, 1, 0);
-        bad_cb = lut_fill(lut_addr, p.cb, 1, p.sign_convention, Pol::kFmt, tid, kUDecWarps * 32, Pol::kIsF8 != 0, &cb_pre);
+        bad_cb = lut_fill(lut_addr, p0.cb, 1, p0.sign_convention, Pol::kFmt, tid, kUDecWarps * 32, Pol::kIsF8 != 0, &cb_pre);
         if (tid == 0) DMM_STAMP(0, 1, 1);
         if (lane == 0) DMM_STAMP(0, 8 + warp, 0);
         named_barrier(4, kUThreads);
@@ -423,11 +443,12 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
             uint32_t count = 1;                                                // TMA, tcgen05.commit
             if (bt >= Plan::kBarEmpty && bt < Plan::kBarFull) count = 4;
             if (bt >= Plan::kBarFull && bt < Plan::kBarFree) count = Pol::kIsF8 ? 4 : 5;  // decoder warps (+ loader)
-            if (bt >= Plan::kBarXReady && bt < Plan::kBarXFree) count = p.x_planes != nullptr ? 1 : kULoadWarps / kULoadTeams;
+            if (bt >= Plan::kBarXReady && bt < Plan::kBarXFree) count = p0.x_planes != nullptr ? 1 : kULoadWarps / kULoadTeams;
             if (bt >= Plan::kBarFree && bt < Plan::kBarXReady) count = TP;  // tcgen05.commit of every issuer of the slot
             if (bt >= Plan::kBarXFree && bt < Plan::kBarDReady) count = NACC * TP;
             if (bt == Plan::kBarDReady) count = NACC * TP;
             if (bt == Plan::kBarDFree) count = 8;
+            if (bt == Plan::kBarGridOk) count = kULoadWarps;
             mbar_init(bar(bt), count);
             if (bt == 0) {
                 flags[0] = 0;
@@ -470,8 +491,11 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
         // falls into the others' look-up bursts instead of all groups idling together.
         if (q != 0) __nanosleep(static_cast<unsigned>(q) * 128u);
         uint32_t sA = 0;  // groups this decoder group has produced
-        int segidx = 0, ebase = 0;
+        int segidx = 0, ebase = 0;  // segments and chunks of this CTA so far (all ops)
         int cidx = 0;  // chunks this group has consumed
+        for (int op = 0; op < n_ops; ++op) {
+        const UmmaParams &p = ch.op[op];
+        DMM_OP_GEOMETRY(p);
         for (int ss = ss_first; ss <= ss_last; ebase += seg_chunks(ss), ++ss, ++segidx) {
             const int len = seg_len(ss);
             const int nchunks_ss = (len + C - 1) / C;
@@ -665,6 +689,23 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
                 if (tid == 0) DMM_STAMP(4, segidx, 2);
             }
         }
+        if (n_ops > 1 && q < 2) {
+            // Chain: tell the other CTAs that this one has finished op `op` (all its atomic adds
+            // are out), once its own loaders have seen op - 1 complete -- the last CTA to arrive
+            // here then knows that nobody polls the counter of op - 1 any more and clears it.
+            __threadfence();
+            named_barrier(2, 256);
+            if (tid == 0) {
+                mbar_wait(bar(Plan::kBarGridOk), static_cast<uint32_t>(op & 1), flags);
+                __threadfence();
+                const unsigned old = atomicAdd(ch.sync + op, 1u);
+                if (old == gridDim.x - 1) {
+                    if (op > 0) ch.sync[op - 1] = 0;
+                    if (op == n_ops - 1) ch.sync[op] = 0;
+                }
+            }
+        }
+        }  // op
     } else if (warp < kUMmaWarp + kUMmaWarps) {
         // =============================== MMA issuers ===============================
         // issuer `me` serves the decoder groups q with q % kNAcc == me and owns accumulator `me`
@@ -677,7 +718,11 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
         if (wi < NACC * TP) {
             const bool leader = elect_one();
             uint32_t cnt0 = 0, cnt1 = 0, cnt2 = 0, cnt3 = 0;  // groups consumed from decoder group 0..3
-            int segidx = 0;
+            int segidx = 0, cbase = 0;  // segments / chunks of this CTA so far (all ops)
+            int eg_base = 0;            // fp8: activation epochs of earlier ops
+            for (int op = 0; op < n_ops; ++op) {
+            const UmmaParams &p = ch.op[op];
+            DMM_OP_GEOMETRY(p);
             const uint32_t idesc = Pol::kIsF8
                                        ? ((1u << 4) | (3u << 7) | (1u << 10) | ((NMMA >> 3) << 17) | ((128u >> 4) << 24))
                                        : ((1u << 4) | ((NMMA >> 3) << 17) | ((128u >> 4) << 24));
@@ -689,13 +734,13 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
             // land in unused columns) or, for the 16-row layout, two of them
             const uint64_t xdesc0 = Pol::kIsF8 ? smem_desc(x_addr, tile_b / 2, NMMA > 32 ? 128u : tile_b / 8)
                                                : smem_desc(x_addr, NMMA * 16, 128);
-            int cur_ep = -1, ep_beg = 0, ep_end = 0;  // fp8: epoch being read and its k-tile range
-            int ep_slot = 0;                          // its buffer, the parity of that buffer's barriers
-            uint32_t ep_par = 0, ep_addr = 0;
+            int cur_ep = -1, ep_beg = 0, ep_end = 0;  // fp8: epoch of this op being read and its k-tile range
+            int ep_slot = eg_base % Plan::kEpochs;    // its buffer, the parity of that buffer's barriers
+            uint32_t ep_par = static_cast<uint32_t>((eg_base / Plan::kEpochs) & 1), ep_addr = 0;
             const uint32_t xdesc_lo = static_cast<uint32_t>(xdesc0), xdesc_hi = static_cast<uint32_t>(xdesc0 >> 32);
             // accumulator of the (first) MMA tile this warp issues
             const uint32_t d_col0 = tmem + static_cast<uint32_t>(((TP == 2 ? tp : 0) * NACC + me) * NMMA);
-            int cbase = 0, jseg = 0;  // chunks / k-tiles of earlier segments
+            int jseg = 0;  // k-tiles of earlier segments of this op
             for (int ss = ss_first; ss <= ss_last; cbase += seg_chunks(ss), jseg += seg_len(ss), ++ss, ++segidx) {
                 const int len = seg_len(ss);
                 const int nchunks = (len + C - 1) / C;
@@ -777,11 +822,13 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
                 if (leader) tc_commit(bar(Plan::kBarDReady));
             }
             if constexpr (Pol::kIsF8) {
-                const int nep = i1 - i0 <= E0 ? 1 : 1 + (i1 - i0 - E0 + E - 1) / E;
+                const int nep = i1 <= i0 ? 0 : (i1 - i0 <= E0 ? 1 : 1 + (i1 - i0 - E0 + E - 1) / E);
                 for (int r = cur_ep < 0 ? 0 : cur_ep; r < nep; ++r)
-                    if (leader) tc_commit(bar(Plan::kBarXFree + r % Plan::kEpochs));
+                    if (leader) tc_commit(bar(Plan::kBarXFree + (eg_base + r) % Plan::kEpochs));
+                eg_base += nep;
                 (void)ep_slot;
             }
+            }  // op
         }
     } else if (warp == kUTmaWarp) {
         // =============================== TMA producer ===============================
@@ -792,6 +839,10 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
             const uint64_t policy = policy_evict_first();
             uint32_t cnt[4] = {0, 0, 0, 0};  // chunks issued per decoder group
             int cbase = 0;
+            for (int op = 0; op < n_ops; ++op) {
+            const UmmaParams &p = ch.op[op];
+            DMM_OP_GEOMETRY(p);
+            (void)p;
             for (int ss = ss_first; ss <= ss_last; cbase += seg_chunks(ss), ++ss) {
                 const int nchunks = seg_chunks(ss), kt0 = seg_kt0(ss);
                 for (int c = 0; c < nchunks; ++c) {
@@ -802,10 +853,11 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
                         mbar_wait(bar(Plan::kBarEmpty + q * RING + slot), ((n_q / RING) - 1) & 1, flags);
                     const uint32_t b = bar(Plan::kBarCode + q * RING + slot);
                     mbar_arrive_expect_tx(b, Plan::kSlotBytes);
-                    tma_load_2d(ring_addr + (q * RING + slot) * Plan::kSlotBytes, &codes_map, (kt0 + c * C) * 32, ss * 16, b, policy);
+                    tma_load_2d(ring_addr + (q * RING + slot) * Plan::kSlotBytes, &ch.map[op], (kt0 + c * C) * 32, ss * 16, b, policy);
                     if (q == 0) ++cnt[0]; else if (q == 1) ++cnt[1]; else if (q == 2) ++cnt[2]; else ++cnt[3];
                 }
             }
+            }  // op
             if (flags[0]) {
                 // A wait gave up somewhere: loads may still be in flight.  Give the last load of
                 // every ring slot a bounded chance to land before the CTA releases its shared memory.
@@ -822,17 +874,36 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
         // loader wl serves the chunks of parity wl (the chunks of issuer wl), one chunk per pass
         grid_dep_wait();
         const int wl = warp - kUMmaWarp - kUMmaWarps;  // warps 20 .. 23
-        if (p.zero_ptr != nullptr) {  // a later kernel will accumulate into it
+        uint32_t cnt0 = 0, cnt1 = 0;  // fp16 policy: groups staged so far for decoder groups wl and wl + 2
+        int cbase = 0;
+        int eg_base = 0;              // fp8 policy: activation epochs of earlier ops
+        for (int op = 0; op < n_ops; ++op) {
+        const UmmaParams &p = ch.op[op];
+        DMM_OP_GEOMETRY(p);
+        if (n_ops > 1) {
+            // Chain: op reads what op - 1 wrote, so wait until every CTA has finished op - 1
+            // (bounded), then let this CTA's own arrival for op go ahead.
+            if (op > 0) {
+                if (lane == 0) grid_wait(ch.sync + (op - 1), gridDim.x, flags);
+                __syncwarp();
+            }
+        }
+        if (p.zero_ptr != nullptr) {  // a later kernel or op will accumulate into it
             constexpr int ZT = kULoadWarps * 32;
             for (long long i = static_cast<long long>(cta) * ZT + wl * 32 + lane; i < p.zero_count;
                  i += static_cast<long long>(gridDim.x) * ZT)
                 p.zero_ptr[i] = 0.f;
         }
+        if (n_ops > 1) {
+            // the CTA's arrival for this op goes out only after this (so that it also covers the
+            // clearing above, whatever share of the op's tiles this CTA has)
+            __threadfence();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar(Plan::kBarGridOk));
+        }
         [[maybe_unused]] const __half *x = reinterpret_cast<const __half *>(p.x);
         const int M = static_cast<int>(p.M);
         const int ppt = M * 4;  // 16-byte pieces per k-tile: (row, 8-k chunk)
-        uint32_t cnt0 = 0, cnt1 = 0;  // groups staged so far for decoder groups wl and wl + 2
-        int cbase = 0;
 
         if constexpr (Pol::kIsF8) {
             // The loaders never touch a barrier per tile: they fill whole epochs of the CTA's
@@ -846,7 +917,7 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
             // loaders may only start once the previous kernel of the stream has finished.
             const int E0 = first_epoch_tiles(E, M);
             const int ntiles = i1 - i0;
-            const int nep = ntiles <= E0 ? 1 : 1 + (ntiles - E0 + E - 1) / E;
+            const int nep = ntiles <= 0 ? 0 : (ntiles <= E0 ? 1 : 1 + (ntiles - E0 + E - 1) / E);
             // two teams of loader warps fill alternate epochs, so that the global-memory latency
             // of one epoch overlaps the plane split of the other
             if (p.x_planes != nullptr && wl == 0 && lane == 0) {
@@ -855,13 +926,14 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
                 // super-tile inside the epoch).
                 const uint8_t *src = reinterpret_cast<const uint8_t *>(p.x_planes);
                 for (int e = 0; e < nep; ++e) {
-                    if (e >= Plan::kEpochs)
-                        mbar_wait(bar(Plan::kBarXFree + e % Plan::kEpochs), static_cast<uint32_t>(((e / Plan::kEpochs) - 1) & 1), flags);
+                    const int eg = eg_base + e;  // epoch number over all ops: buffer and barrier phase
+                    if (eg >= Plan::kEpochs)
+                        mbar_wait(bar(Plan::kBarXFree + eg % Plan::kEpochs), static_cast<uint32_t>(((eg / Plan::kEpochs) - 1) & 1), flags);
                     const int t_lo = e == 0 ? 0 : E0 + (e - 1) * E;
                     const int e_len = e == 0 ? E0 : E;
                     const int nt = ntiles - t_lo < e_len ? ntiles - t_lo : e_len;
-                    const uint32_t ebuf = x_addr + (e % Plan::kEpochs) * Plan::kEpochBytes;
-                    const uint32_t b = bar(Plan::kBarXReady + e % Plan::kEpochs);
+                    const uint32_t ebuf = x_addr + (eg % Plan::kEpochs) * Plan::kEpochBytes;
+                    const uint32_t b = bar(Plan::kBarXReady + eg % Plan::kEpochs);
                     mbar_arrive_expect_tx(b, static_cast<uint32_t>(nt) * tile_b);
                     for (int t = 0; t < nt;) {
                         const int gt = i0 + t_lo + t;
@@ -873,21 +945,23 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
                 }
                 if (flags[0]) {  // a wait gave up: let the copies in flight land before the CTA exits
                     for (int e = nep > Plan::kEpochs ? nep - Plan::kEpochs : 0; e < nep; ++e)
-                        mbar_wait_limit(bar(Plan::kBarXReady + e % Plan::kEpochs), static_cast<uint32_t>((e / Plan::kEpochs) & 1),
-                                        20ll * 1000 * 1000);
+                        mbar_wait_limit(bar(Plan::kBarXReady + (eg_base + e) % Plan::kEpochs),
+                                        static_cast<uint32_t>(((eg_base + e) / Plan::kEpochs) & 1), 20ll * 1000 * 1000);
                 }
             }
             const int lt = (wl / kULoadTeams) * 32 + lane;
             constexpr int LT = kULoadWarps / kULoadTeams * 32;
-            for (int e = wl % kULoadTeams; p.x_planes == nullptr && e < nep; e += kULoadTeams) {
+            // (team by the epoch number over all ops, so that the teams keep alternating across ops)
+            for (int e = ((wl % kULoadTeams) - eg_base) & (kULoadTeams - 1); p.x_planes == nullptr && e < nep; e += kULoadTeams) {
+                const int eg = eg_base + e;
                 if (wl == 0 && lane == 0) DMM_STAMP(3, e, 0);
-                if (e >= Plan::kEpochs)
-                    mbar_wait(bar(Plan::kBarXFree + e % Plan::kEpochs), static_cast<uint32_t>(((e / Plan::kEpochs) - 1) & 1), flags);
+                if (eg >= Plan::kEpochs)
+                    mbar_wait(bar(Plan::kBarXFree + eg % Plan::kEpochs), static_cast<uint32_t>(((eg / Plan::kEpochs) - 1) & 1), flags);
                 const int t_lo = e == 0 ? 0 : E0 + (e - 1) * E;
                 const int e_len = e == 0 ? E0 : E;
                 const int nt = ntiles - t_lo < e_len ? ntiles - t_lo : e_len;
                 const int npieces = nt * ppt;
-                const uint32_t ebuf = x_addr + (e % Plan::kEpochs) * Plan::kEpochBytes;
+                const uint32_t ebuf = x_addr + (eg % Plan::kEpochs) * Plan::kEpochBytes;
                 for (int pbase = 0; pbase < npieces; pbase += LT * U) {
                     uint32_t h[U][4];
                     uint32_t dst[U];
@@ -917,9 +991,10 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
                 }
                 fence_async_smem();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(bar(Plan::kBarXReady + e % Plan::kEpochs));
+                if (lane == 0) mbar_arrive(bar(Plan::kBarXReady + eg % Plan::kEpochs));
                 if (wl == 0 && lane == 0) DMM_STAMP(3, e, 1);
             }
+            eg_base += nep;
         } else {
             // fp16 activations: cp.async straight into the stage, two chunks in flight
             uint32_t pend_q[2] = {0, 0}, pend_cn[2] = {0, 0}, pend_ng[2] = {0, 0};
@@ -965,6 +1040,7 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const UmmaParams p,
                 retire();
             }
         }
+        }  // op
     }
 
     tc_fence_before();
@@ -1003,35 +1079,70 @@ inline int make_codes_map(CUtensorMap *map, const void *codes, long long N, long
     return r == CUDA_SUCCESS ? 0 : cudaErrorInvalidValue;
 }
 
-template <class Pol, int NMMA>
-inline int launch_umma_one(const UmmaParams &p_in, int num_sms, bool pdl, cudaStream_t stream) {
+template <class Pol, int NMMA, bool kChain>
+inline int launch_umma_ops(const UmmaParams *ops, int n_ops, unsigned *sync, int num_sms, bool pdl, cudaStream_t stream);
+
+// Launches `n_ops` products as one kernel.  n_ops == 1 (kChain false): the plain case, grid =
+// min(tiles, SMs).  A chain (kChain true): grid = SMs for every op and a cooperative launch, because
+// the CTAs wait for one another between ops and must all be resident; `sync` = n_ops zeroed counters.
+template <class Pol, int NMMA, bool kChain>
+inline int launch_umma_ops(const UmmaParams *ops, int n_ops, unsigned *sync, int num_sms, bool pdl, cudaStream_t stream) {
     using Plan = UmmaPlan<Pol, NMMA>;
-    UmmaParams p = p_in;
-    p.dyn_smem_bytes = Plan::kDynBytes;
-    auto kernel = umma_kernel<Pol, NMMA>;
+    auto kernel = umma_kernel<Pol, NMMA, kChain>;
     cudaError_t err =
         cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Plan::kDynBytes));
     if (err != cudaSuccess) return err;
-    const long long KT = p.K / 32, NS = p.N / 16, SST = (NS + 15) / 16;
-    const long long T = SST * KT;
-    if (T >= (1ll << 31)) return DMM_ERR_SHAPE;
-    const unsigned grid = static_cast<unsigned>(T < num_sms ? T : num_sms);
-    p.part.a = static_cast<int>(T / grid);
-    p.part.b = static_cast<int>(T % grid);
-    CUtensorMap map;
-    const int rc = make_codes_map(&map, p.codes, p.N, p.K, Pol::kC);
-    if (rc) return rc;
+    UmmaChainT<kChain ? kMaxOps : 1> ch = {};
+    ch.n_ops = n_ops;
+    ch.sync = sync;
+    unsigned grid = static_cast<unsigned>(num_sms);
+    if (!kChain) {
+        const long long T = ((ops[0].N / 16 + 15) / 16) * (ops[0].K / 32);
+        if (T < num_sms) grid = static_cast<unsigned>(T);
+    }
+    for (int i = 0; i < n_ops; ++i) {
+        UmmaParams &p = ch.op[i];
+        p = ops[i];
+        p.dyn_smem_bytes = Plan::kDynBytes;
+        const long long KT = p.K / 32, NS = p.N / 16, SST = (NS + 15) / 16;
+        const long long T = SST * KT;
+        if (T >= (1ll << 31)) return DMM_ERR_SHAPE;
+        p.part.a = static_cast<int>(T / grid);
+        p.part.b = static_cast<int>(T % grid);
+        const int rc = make_codes_map(&ch.map[i], p.codes, p.N, p.K, Pol::kC);
+        if (rc) return rc;
+    }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
     cfg.blockDim = dim3(kUThreads);
     cfg.dynamicSmemBytes = Plan::kDynBytes;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchAttribute attr[2];
+    int na = 0;
+    if (pdl) {
+        attr[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    if (kChain) {
+        attr[na].id = cudaLaunchAttributeCooperative;
+        attr[na].val.cooperative = 1;
+        ++na;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, kernel, p, map);
+    cfg.numAttrs = na;
+    return cudaLaunchKernelEx(&cfg, kernel, ch);
+}
+
+template <class Pol, int NMMA>
+inline int launch_umma_one(const UmmaParams &p, int num_sms, bool pdl, cudaStream_t stream) {
+    return launch_umma_ops<Pol, NMMA, false>(&p, 1, nullptr, num_sms, pdl, stream);
+}
+
+// A chain of up to kMaxOps dependent products, batch <= 8 (fp8 policy, activations split in the kernel).
+inline int launch_umma_chain(const UmmaParams *ops, int n_ops, unsigned *sync, int num_sms, bool pdl, cudaStream_t stream) {
+    if (n_ops < 2 || n_ops > kMaxOps) return DMM_ERR_ARG;
+    return launch_umma_ops<PolF8, 32, true>(ops, n_ops, sync, num_sms, pdl, stream);
 }
 
 // From this batch size on the fp8-operand path splits the activations into planes with

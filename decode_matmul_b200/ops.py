@@ -127,6 +127,39 @@ def decode_matmul_fused(x, weights_compressed, codebook_fp16, scale, output, *, 
     return output
 
 
+def decode_matmul_chain(ops, codebook_fp16, *, sign_convention=_lib.SIGN_SLOW, pdl=False):
+    """Up to ``CHAIN_MAX_OPS`` dependent products in one launch (``dmm_f16_chain``).
+
+    ``ops`` is a list of dicts with the keyword arguments of :func:`decode_matmul_fused` for one
+    product each: ``x``, ``weights_compressed``, ``scale``, ``output`` and optionally ``x_kind``,
+    ``x_gap``, ``zero``.  Every product is ADDED to its ``output`` with atomic adds, and op k + 1
+    may read what op k wrote.  Batch at most 8; needs the whole GPU (cooperative launch)."""
+    _req(2 <= len(ops) <= _lib.CHAIN_MAX_OPS, f"a chain has 2 to {_lib.CHAIN_MAX_OPS} ops")
+    _check_input(codebook_fp16, "codebook_fp16", torch.float16)
+    arr = (_lib.ChainOp * len(ops))()
+    M = ops[0]["x"].shape[0]
+    for i, op in enumerate(ops):
+        x, w, out = op["x"], op["weights_compressed"], op["output"]
+        x_kind = op.get("x_kind", _lib.X_F32)
+        _check_input(x, "x", torch.float16 if x_kind == _lib.X_F16 else torch.float32)
+        _check_input(w, "weights_compressed", torch.int16)
+        _check_input(out, "output", torch.float32)
+        N, K = w.size(0), w.size(1) * 8
+        _req(x.dim() == 2 and x.shape[0] == M and x.shape[1] >= K, "x must be [M, >= K]")
+        _req(tuple(out.shape) == (M, N), "output must have shape [M, N]")
+        zero = op.get("zero")
+        if zero is not None:
+            _check_input(zero, "zero", torch.float32)
+        arr[i] = _lib.ChainOp(x.data_ptr(), x_kind, x.shape[1], op.get("x_gap", 0), w.data_ptr(), float(op["scale"]),
+                              out.data_ptr(), N, K, None if zero is None else zero.data_ptr(),
+                              0 if zero is None else zero.numel())
+    dev = ops[0]["x"].device
+    with torch.cuda.device(dev):
+        rc = _lib.lib().dmm_f16_chain(ctypes.byref(arr), len(ops), _ptr(codebook_fp16), M, sign_convention,
+                                      _lib.FLAG_PDL if pdl else 0, _stream_ptr(dev))
+    _lib.check(rc, "decode_matmul_chain")
+
+
 def decode_matmul_fp16_noalloc(x, weights_compressed, codebook_fp16, scale, output, *,
                                sign_convention=_lib.SIGN_SLOW, accumulate=False, pdl=False):
     """``decode_matmul_fp16`` for programs that cannot let the library allocate device memory

@@ -131,6 +131,37 @@ int dmm_f16_fused(const void *x, int x_kind, int64_t x_ld, int64_t x_gap, const 
                   int64_t zero_count, void *workspace, size_t workspace_bytes, void *stream);
 
 /*
+ * A chain of dependent products in ONE launch.  (No counterpart in the reference.)
+ *
+ * ops[k] is one dmm_f16_fused product, out_k += scale_k * f(x_k) . W_k^T, where op k + 1 may
+ * read what op k wrote (the next layer of a model).  Launched one by one, every layer pays
+ * the launch, the table build and the filling and draining of the pipeline; in a chain the CTAs
+ * stay resident, only the activation loaders wait at an op boundary (until every CTA has
+ * finished the previous op), and the weight decoders are already working on the next op.
+ * Rules: 2 <= n_ops <= DMM_CHAIN_MAX_OPS; batch M <= 8; tile layout; one codebook and sign
+ * convention for all ops; results are ADDED to out_k with atomic adds (as DMM_FLAG_ATOMIC: out_k must
+ * hold the value to add to, e.g. be cleared by the zero_ptr of an earlier op); flags: DMM_FLAG_PDL
+ * only.  The CTAs wait for one another, so the kernel is launched cooperatively with one CTA per
+ * SM: it needs the whole GPU, and two chains must not run at the same time on one device.
+ * All device-side waits are bounded (DMM_STATUS_WAIT_TIMEOUT); after a timeout call
+ * dmm_status() before the next chain (it also clears the chain's counters).
+ */
+#define DMM_CHAIN_MAX_OPS 8
+typedef struct dmm_chain_op {
+    const void *x;        /* activations of this op, see x_kind */
+    int x_kind;           /* DMM_X_F16 / DMM_X_F32 / DMM_X_F32_SILU_MUL */
+    int64_t x_ld, x_gap;  /* as in dmm_f16_fused */
+    const int16_t *codes; /* tiled codes [N, K/8] */
+    float scale;
+    float *out;           /* [M, N] fp32, accumulated into */
+    int64_t N, K;
+    float *zero_ptr;      /* optional buffer cleared by this op (see dmm_f16_fused) */
+    int64_t zero_count;
+} dmm_chain_op;
+int dmm_f16_chain(const dmm_chain_op *ops, int n_ops, const void *cb16, int64_t M, int sign_convention,
+                  unsigned flags, void *stream);
+
+/*
  * dmm_f16 for callers that must not allocate.  (No counterpart in the reference.)
  *
  * Some host programs cannot let a library call cudaMalloc on their behalf: a serving

@@ -351,3 +351,73 @@ def test_fast_entry_point_and_layout(M, N, K, e8p):
     w = dmm.decode_weights(_dev(o.fast_pack(codes)), _dev(e8p), layout=dmm.LAYOUT_FAST, sign_convention=dmm.SIGN_FAST)
     assert np.array_equal(w.cpu().numpy(), o.decode_weights(codes, e8p, o.SIGN_FAST))
     assert dmm.status() == 0
+
+
+@pytest.mark.parametrize("M,hid,ffn", [(1, 512, 1024), (3, 256, 2048), (2, 4096, 11008)])
+def test_chain_of_dependent_products_matches_separate_launches(M, hid, ffn):
+    """dmm_f16_chain: two transformer blocks (8 dependent products, fp32 and SiLU inputs, buffers
+    cleared on the way) in ONE cooperative launch against the same products launched one by one;
+    shapes include ops with fewer tiles than CTAs.  Run twice: the arrival counters must be clean."""
+    torch.manual_seed(M + hid)
+    cb = dmm.synthetic_codebook(42, "cuda")
+
+    def rnd(n, k):
+        return torch.randint(-32768, 32768, (n, k // 8), dtype=torch.int16, device="cuda")
+
+    nq = hid + 256
+    Wq, Wo, Wg, Wd = rnd(nq, hid), rnd(hid, hid), rnd(2 * ffn, hid), rnd(hid, ffn)
+    sc = 2.0 ** -9
+    h0 = torch.randn(M, hid, device="cuda") * 0.5
+
+    def run(chain):
+        h = h0.clone()
+        a = torch.zeros(M, nq, device="cuda")
+        g = torch.full((M, 2 * ffn), 7.0, device="cuda")  # must be cleared by the first op
+        ops = [dict(x=h, weights_compressed=Wq, scale=sc, output=a, zero=g),
+               dict(x=a, weights_compressed=Wo, scale=sc, output=h),
+               dict(x=h, weights_compressed=Wg, scale=sc, output=g, zero=a),
+               dict(x=g, weights_compressed=Wd, scale=sc, output=h, x_kind=dmm.X_F32_SILU_MUL, x_gap=ffn)]
+        if chain:
+            dmm.decode_matmul_chain(ops + ops, cb, pdl=True)
+        else:
+            for op in ops + ops:
+                dmm.decode_matmul_fused(op["x"], op["weights_compressed"], cb, op["scale"], op["output"],
+                                        x_kind=op.get("x_kind", dmm.X_F32), x_gap=op.get("x_gap", 0), zero=op.get("zero"),
+                                        accumulate=True, atomic=True)
+        torch.cuda.synchronize()
+        return h
+
+    want = run(False)
+    for _ in range(2):
+        got = run(True)
+        assert dmm.status() == 0
+        tol = 2e-3 * max(1.0, float(want.abs().max()))
+        assert float((got - want).abs().max()) <= tol
+
+
+def test_chain_argument_errors():
+    cb = dmm.synthetic_codebook(42, "cuda")
+    w = torch.zeros((64, 8), dtype=torch.int16, device="cuda")
+    x = torch.zeros((9, 64), device="cuda")
+    out = torch.zeros((9, 64), device="cuda")
+    op = dict(x=x, weights_compressed=w, scale=1.0, output=out)
+    with pytest.raises(RuntimeError):
+        dmm.decode_matmul_chain([op], cb)          # a chain has at least two ops
+    with pytest.raises(RuntimeError):
+        dmm.decode_matmul_chain([op, op], cb)      # batch 9 > 8
+
+
+def test_linear_stack_chained_step_matches_plain():
+    """The optional chained form of the fused step (two blocks per cooperative launch)."""
+    from decode_matmul_b200.linear import LinearStack
+
+    cfg = dict(hidden=512, kv_heads=2, head_dim=64, ffn=1024, layers=4)
+    stack = LinearStack(cfg, dmm.synthetic_codebook(42), "cuda", seed=7, scale=2.0 ** -8)
+    torch.manual_seed(11)
+    h0 = torch.randn(1, 512, device="cuda")
+    stack.chain_blocks = 2
+    h_chain = stack.step(h0.clone(), fused=True)
+    stack.chain_blocks = 0
+    h_fused = stack.step(h0.clone(), fused=True)
+    assert dmm.status() == 0
+    assert torch.allclose(h_chain, h_fused, rtol=2e-3, atol=2e-3)

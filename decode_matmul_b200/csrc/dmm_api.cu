@@ -21,6 +21,7 @@ struct DeviceState {
     void *retile = nullptr;     // library-owned buffer for codes re-tiled from the fast layout
     size_t retile_bytes = 0;
     unsigned *chain_sync = nullptr;  // arrival counters of dmm_f16_chain (zero between launches)
+    unsigned *xrank_counter = nullptr;  // number of dmm_xrank_barrier calls executed on this device
 };
 
 static std::mutex g_mutex;
@@ -174,10 +175,18 @@ static long long *g_trace = nullptr;  // device buffer for clock stamps (debug b
 
 // tcgen05 path: one launch per chunk of 64 batch columns (32 for the fp6/fp8 operand policy,
 // preceded by planes_kernel when the chunk has at least kPlanesMinBatch rows).
+// Tensor-parallel extras of one call (dmm_f16_fused_tp).
+struct TpArgs {
+    float *const *peer_out = nullptr;
+    int n_peers = 0;
+    float *move_src = nullptr, *move_dst = nullptr;
+    long long move_count = 0;
+};
+
 static int run_umma(bool f8, const void *x, int x_kind, long long x_ld, long long x_gap, const void *codes,
                     const void *cb16, float scale, float *out, long long M, long long N, long long K,
                     int sign_convention, unsigned flags, void *workspace, size_t workspace_bytes, cudaStream_t stream,
-                    float *zero_ptr = nullptr, long long zero_count = 0) {
+                    float *zero_ptr = nullptr, long long zero_count = 0, const TpArgs *tp = nullptr) {
     DeviceState *d = nullptr;
     int rc = current_device_state(&d);
     if (rc) return rc;
@@ -216,6 +225,15 @@ static int run_umma(bool f8, const void *x, int x_kind, long long x_ld, long lon
         if (m0 == 0) {
             p.zero_ptr = zero_ptr;
             p.zero_count = zero_count;
+            if (tp != nullptr) {
+                p.move_src = tp->move_src;
+                p.move_dst = tp->move_dst;
+                p.move_count = tp->move_count;
+            }
+        }
+        if (tp != nullptr) {
+            p.n_peers = tp->n_peers;
+            for (int r = 0; r < tp->n_peers; ++r) p.peer_out[r] = tp->peer_out[r] + static_cast<size_t>(m0) * N;
         }
 #ifdef DMM_TRACE
         p.trace = g_trace;
@@ -321,6 +339,69 @@ int dmm_f16(const void *x, const int16_t *codes, const void *cb16, float scale, 
             size_t workspace_bytes, void *stream) {
     return dmm_f16_fused(x, DMM_X_F16, K, 0, codes, cb16, scale, out, M, N, K, sign_convention, layout, path, flags,
                          nullptr, 0, workspace, workspace_bytes, stream);
+}
+
+int dmm_f16_fused_tp(const void *x, int x_kind, int64_t x_ld, int64_t x_gap, const int16_t *codes, const void *cb16,
+                     float scale, float *const *peer_out, int n_peers, int64_t M, int64_t N, int64_t K,
+                     int sign_convention, unsigned flags, float *zero_ptr, int64_t zero_count, float *move_src,
+                     float *move_dst, int64_t move_count, void *stream) {
+    if (!peer_out) return DMM_ERR_NULL;
+    if (n_peers < 1 || n_peers > 8) return DMM_ERR_ARG;
+    for (int r = 0; r < n_peers; ++r)
+        if (!peer_out[r] || !aligned16(peer_out[r])) return peer_out[r] ? DMM_ERR_ALIGN : DMM_ERR_NULL;
+    int rc = check_common(x, codes, cb16, peer_out[0], M, N, K, sign_convention, DMM_LAYOUT_TILE);
+    if (rc) return rc;
+    if (x_kind != DMM_X_F16 && x_kind != DMM_X_F32 && x_kind != DMM_X_F32_SILU_MUL) return DMM_ERR_ARG;
+    if (x_ld < K || x_ld % 8 != 0 || x_gap % 4 != 0 || (x_kind == DMM_X_F32_SILU_MUL && x_gap + K > x_ld))
+        return DMM_ERR_SHAPE;
+    if (flags & ~DMM_FLAG_PDL) return DMM_ERR_ARG;
+    if (zero_count < 0 || (zero_count > 0 && zero_ptr == nullptr)) return DMM_ERR_ARG;
+    if (move_count < 0 || (move_count > 0 && (move_src == nullptr || move_dst == nullptr))) return DMM_ERR_ARG;
+    TpArgs tp;
+    tp.peer_out = peer_out;
+    tp.n_peers = n_peers;
+    tp.move_src = move_src;
+    tp.move_dst = move_dst;
+    tp.move_count = move_count;
+    return run_umma(true, x, x_kind, x_ld, x_gap, codes, cb16, scale, peer_out[0], M, N, K, sign_convention,
+                    flags | DMM_FLAG_ATOMIC | DMM_FLAG_ACCUMULATE, nullptr, 0, static_cast<cudaStream_t>(stream), zero_ptr,
+                    zero_count, &tp);
+}
+
+int dmm_xrank_barrier(unsigned *const *peer_flags, int rank, int world, void *stream) {
+    if (!peer_flags) return DMM_ERR_NULL;
+    if (world < 1 || world > 8 || rank < 0 || rank >= world) return DMM_ERR_ARG;
+    DeviceState *d = nullptr;
+    int rc = current_device_state(&d);
+    if (rc) return rc;
+    {
+        std::lock_guard<std::mutex> lock(g_mutex);
+        if (d->xrank_counter == nullptr) {
+            cudaError_t err = cudaMalloc(reinterpret_cast<void **>(&d->xrank_counter), 256);
+            if (err != cudaSuccess) return err;
+            err = cudaMemset(d->xrank_counter, 0, 256);
+            if (err != cudaSuccess) return err;
+        }
+    }
+    XrankBarrierParams bp = {};
+    for (int r = 0; r < world; ++r) {
+        if (!peer_flags[r]) return DMM_ERR_NULL;
+        bp.flags[r] = peer_flags[r];
+    }
+    bp.counter = d->xrank_counter;
+    bp.rank = rank;
+    bp.world = world;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(1);
+    cfg.blockDim = dim3(32);
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return cudaLaunchKernelEx(&cfg, xrank_barrier_kernel, bp);
 }
 
 int dmm_f16_chain(const dmm_chain_op *ops, int n_ops, const void *cb16, int64_t M, int sign_convention,

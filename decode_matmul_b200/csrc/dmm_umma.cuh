@@ -276,6 +276,14 @@ struct UmmaParams {
     const void *x_planes;  // fp8 policy, optional: the E5M2 planes of x already split by planes_kernel, in the
                            // layout of the epoch buffers ([k-tile][k-half][plane][row][16 B]); the
                            // kernel then copies them with bulk copies and its loaders do no arithmetic
+    // Tensor-parallel epilogue (optional): with n_peers > 0 the atomic adds go to the same buffer on
+    // every rank (peer_out[r], this rank's own included) instead of `out`, over NVLink peer memory,
+    // so that the sum over ranks needs no separate all-reduce; see dmm_f16_fused_tp.
+    float *peer_out[8];
+    int n_peers;
+    float *move_src;     // optional: move_dst[i] += move_src[i], then move_src[i] = 0 (this rank's copy of the
+    float *move_dst;     // residual stream changing buffers), done by the loaders like the clearing below
+    long long move_count;
     float *zero_ptr;     // optional: buffer this kernel clears on its way (see dmm_f16_fused)
     long long zero_count;
     Part32 part;         // tiles per CTA: part.a = T / grid, part.b = T % grid
@@ -342,6 +350,46 @@ __device__ __forceinline__ uint2 next_plane(uint32_t (&h)[4]) {
         h[j] = *reinterpret_cast<uint32_t *>(&rr);
     }
     return bytes;
+}
+
+// Barrier between the ranks of a tensor-parallel group, one process per GPU: thread t tells rank t
+// that this rank has arrived (a release store of the barrier's number into slot `rank` of rank t's
+// flag array, through peer memory) and waits, bounded, until rank t has told this rank the same.
+// The number comes from a counter in this GPU's memory that every execution increments, so a
+// captured launch can be replayed.  The ranks are different GPUs, hence run concurrently.
+struct XrankBarrierParams {
+    unsigned *flags[8];  // flags[t]: rank t's array of `world` words (peer pointers; [rank] is local)
+    unsigned *counter;   // this rank's barrier counter (local)
+    int rank, world;
+};
+__global__ void __launch_bounds__(32) xrank_barrier_kernel(const XrankBarrierParams bp) {
+    // Launched with programmatic stream serialization: the kernel after it may start at once (its
+    // weight decode does not depend on other ranks; its activation loaders wait for this kernel to
+    // finish), and this kernel itself may have started before the one before it has finished.
+    grid_dep_launch();
+    grid_dep_wait();
+    const int t = threadIdx.x;
+    unsigned e = 0;
+    if (t == 0) e = atomicAdd(bp.counter, 1u) + 1u;
+    e = __shfl_sync(0xffffffffu, e, 0);
+    __threadfence_system();  // everything this GPU wrote before (peer atomics of the kernel before) first
+    if (t < bp.world) {
+        unsigned *dst = bp.flags[t] + bp.rank;
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(dst), "r"(e) : "memory");
+        const unsigned *mine = bp.flags[bp.rank] + t;
+        const long long t0 = clock64();
+        for (;;) {
+            unsigned v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+            if (static_cast<int>(v - e) >= 0) break;
+            if (clock64() - t0 > kWaitLimitCycles) {
+                raise_status(DMM_STATUS_WAIT_TIMEOUT);
+                break;
+            }
+            __nanosleep(100);
+        }
+    }
+    __threadfence_system();
 }
 
 // Splits the activations of one call into E5M2 planes ONCE, in the layout the tcgen05 kernel's
@@ -624,9 +672,18 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const __grid_constan
                 const int ptid = q * 128 + trow;
                 if (p.atomic_reduce) {
                     if (n < p.N) {
+                        if (p.n_peers > 0) {
+                            // the same element on every rank: system-scope adds over NVLink peer memory
+                            for (int r = 0; r < p.n_peers; ++r) {
 #pragma unroll
-                        for (int b = 0; b < NB; ++b)
-                            if (b < p.M) atomicAdd(p.out + b * p.N + n, p.scale * v[b]);
+                                for (int b = 0; b < NB; ++b)
+                                    if (b < p.M) atomicAdd_system(p.peer_out[r] + b * p.N + n, p.scale * v[b]);
+                            }
+                        } else {
+#pragma unroll
+                            for (int b = 0; b < NB; ++b)
+                                if (b < p.M) atomicAdd(p.out + b * p.N + n, p.scale * v[b]);
+                        }
                     }
                 } else if (full) {
                     if (n < p.N) {
@@ -893,6 +950,15 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const __grid_constan
             for (long long i = static_cast<long long>(cta) * ZT + wl * 32 + lane; i < p.zero_count;
                  i += static_cast<long long>(gridDim.x) * ZT)
                 p.zero_ptr[i] = 0.f;
+        }
+        if (p.move_count > 0) {
+            constexpr int ZT = kULoadWarps * 32;
+            for (long long i = static_cast<long long>(cta) * ZT + wl * 32 + lane; i < p.move_count;
+                 i += static_cast<long long>(gridDim.x) * ZT) {
+                const float v = __ldcg(p.move_src + i);
+                p.move_src[i] = 0.f;
+                atomicAdd(p.move_dst + i, v);  // other ranks may already be adding their products
+            }
         }
         if (n_ops > 1) {
             // the CTA's arrival for this op goes out only after this (so that it also covers the

@@ -134,8 +134,81 @@ class LinearStack:
             self._buf_key = key
         return self._buf
 
+    def _peer_state(self, batch: int):
+        """Symmetric (peer-mapped) buffers for the tensor-parallel step: two copies of the residual
+        stream and the flag words of the rank barrier.  None when symmetric memory cannot be set
+        up (or DMM_TP_PEER=0): the step then sums with NCCL all-reduce."""
+        import os
+
+        key = (batch,)
+        if getattr(self, "_peer_key", None) == key:
+            return self._peer
+        self._peer_key, self._peer = key, None
+        if self.world == 1 or os.environ.get("DMM_TP_PEER", "1") == "0":
+            return None
+        ok = torch.zeros(1, device=self.device)
+        try:
+            import torch.distributed._symmetric_memory as symm
+
+            group = self.group if self.group is not None else torch.distributed.group.WORLD
+            res = symm.empty((2, batch, self.hidden), dtype=torch.float32, device=self.device)
+            flags = symm.empty((64,), dtype=torch.int32, device=self.device)
+            res.zero_()
+            flags.zero_()
+            h_res, h_flags = symm.rendezvous(res, group), symm.rendezvous(flags, group)
+            nbytes = batch * self.hidden * 4
+            peer = dict(res=res, flags=flags, cur=0,
+                        res_ptrs=[[int(ptr) + i * nbytes for ptr in h_res.buffer_ptrs] for i in range(2)],
+                        flag_ptrs=[int(ptr) for ptr in h_flags.buffer_ptrs])
+            ok.fill_(1)
+        except Exception:  # no peer mapping on this system: every rank must fall back together
+            peer = None
+        torch.distributed.all_reduce(ok, op=torch.distributed.ReduceOp.MIN, group=self.group)
+        torch.cuda.synchronize(self.device)
+        self._peer = peer if float(ok.item()) == 1.0 else None
+        return self._peer
+
+    def _step_fused_peer(self, h: torch.Tensor, peer) -> torch.Tensor:
+        """Tensor-parallel fused step without collectives: the row-parallel kernels add their
+        partial products into the residual buffer of EVERY rank through peer memory, and a
+        barrier kernel orders the ranks.  The residual stream alternates between two buffers, so a
+        rank never adds into a buffer that a slower rank still reads (the kernel that adds first
+        moves this rank's own copy over and leaves the old buffer zero)."""
+        from .ops import decode_matmul_fused as mm
+        from .ops import decode_matmul_fused_tp as mm_tp
+        from .ops import xrank_barrier
+
+        B = h.shape[0]
+        buf = self._buffers(B)
+        a, g = buf["a"], buf["g"]
+        hid_loc, ffn_loc = self.hidden // self.world, self.ffn // self.world
+        res, cur = peer["res"], peer["cur"]
+        res[cur].copy_(h)  # the other buffer is zero (invariant kept by every row-parallel kernel)
+        a.zero_()
+        kw = dict(accumulate=True, atomic=True, pdl=True)
+        for blk in self.layers:
+            q, o, gu, dn = blk["qkv"], blk["o"], blk["gate_up"], blk["down"]
+            mm(res[cur], q.codes, q.codebook, q.scale, a, x_kind=_lib.X_F32, zero=g, **kw)
+            mm_tp(a, o.codes, o.codebook, o.scale, peer["res_ptrs"][1 - cur], (B, self.hidden), x_kind=_lib.X_F32, pdl=True,
+                  move_src=res[cur], move_dst=res[1 - cur])
+            xrank_barrier(peer["flag_ptrs"], self.rank, self.device)
+            cur = 1 - cur
+            mm(res[cur], gu.codes, gu.codebook, gu.scale, g, x_kind=_lib.X_F32, zero=a, **kw)
+            mm_tp(g, dn.codes, dn.codebook, dn.scale, peer["res_ptrs"][1 - cur], (B, self.hidden),
+                  x_kind=_lib.X_F32_SILU_MUL, x_gap=ffn_loc, pdl=True, move_src=res[cur], move_dst=res[1 - cur])
+            xrank_barrier(peer["flag_ptrs"], self.rank, self.device)
+            cur = 1 - cur
+        h.copy_(res[cur])
+        res[cur].zero_()  # restores the starting state: both buffers zero, so `cur` may restart at 0
+        return h
+
     def _step_fused(self, h: torch.Tensor) -> torch.Tensor:
         from .ops import decode_matmul_fused as mm
+
+        if self.world > 1 and h.shape[0] <= 32:
+            peer = self._peer_state(h.shape[0])
+            if peer is not None:
+                return self._step_fused_peer(h, peer)
 
         buf = self._buffers(h.shape[0])
         a, g, po, pd = buf["a"], buf["g"], buf["po"], buf["pd"]

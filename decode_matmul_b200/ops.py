@@ -127,6 +127,45 @@ def decode_matmul_fused(x, weights_compressed, codebook_fp16, scale, output, *, 
     return output
 
 
+def decode_matmul_fused_tp(x, weights_compressed, codebook_fp16, scale, peer_out_ptrs, out_shape, *, x_kind=_lib.X_F32,
+                           x_gap=0, sign_convention=_lib.SIGN_SLOW, pdl=False, zero=None, move_src=None, move_dst=None):
+    """Row-parallel product whose epilogue adds the partial result into the same [M, N] fp32 buffer
+    on every rank (``dmm_f16_fused_tp``).  ``peer_out_ptrs``: device addresses of that buffer on each
+    rank (this rank's own included), e.g. from symmetric memory; ``out_shape`` = (M, N).
+    ``move_src`` / ``move_dst``: local fp32 tensors, ``move_dst += move_src; move_src = 0`` first."""
+    _check_input(x, "x", torch.float16 if x_kind == _lib.X_F16 else torch.float32)
+    _check_input(weights_compressed, "weights_compressed", torch.int16)
+    _check_input(codebook_fp16, "codebook_fp16", torch.float16)
+    M, ld = x.shape
+    N, K = weights_compressed.size(0), weights_compressed.size(1) * 8
+    _req(tuple(out_shape) == (M, N), "out_shape must be (M, N)")
+    _req(1 <= len(peer_out_ptrs) <= 8, "1 to 8 ranks")
+    if zero is not None:
+        _check_input(zero, "zero", torch.float32)
+    n_move = 0
+    if move_src is not None:
+        _check_input(move_src, "move_src", torch.float32)
+        _check_input(move_dst, "move_dst", torch.float32)
+        _req(move_src.numel() == move_dst.numel(), "move_src and move_dst differ in size")
+        n_move = move_src.numel()
+    ptrs = (ctypes.c_void_p * len(peer_out_ptrs))(*[int(v) for v in peer_out_ptrs])
+    with torch.cuda.device(x.device):
+        rc = _lib.lib().dmm_f16_fused_tp(_ptr(x), x_kind, ld, x_gap, _ptr(weights_compressed), _ptr(codebook_fp16),
+                                         float(scale), ptrs, len(peer_out_ptrs), M, N, K, sign_convention,
+                                         _lib.FLAG_PDL if pdl else 0, None if zero is None else _ptr(zero),
+                                         0 if zero is None else zero.numel(), None if n_move == 0 else _ptr(move_src),
+                                         None if n_move == 0 else _ptr(move_dst), n_move, _stream_ptr(x.device))
+    _lib.check(rc, "decode_matmul_fused_tp")
+
+
+def xrank_barrier(peer_flag_ptrs, rank, device):
+    """Barrier kernel between the ranks of a tensor-parallel group (``dmm_xrank_barrier``)."""
+    ptrs = (ctypes.c_void_p * len(peer_flag_ptrs))(*[int(v) for v in peer_flag_ptrs])
+    with torch.cuda.device(device):
+        rc = _lib.lib().dmm_xrank_barrier(ptrs, rank, len(peer_flag_ptrs), _stream_ptr(device))
+    _lib.check(rc, "xrank_barrier")
+
+
 def decode_matmul_chain(ops, codebook_fp16, *, sign_convention=_lib.SIGN_SLOW, pdl=False):
     """Up to ``CHAIN_MAX_OPS`` dependent products in one launch (``dmm_f16_chain``).
 

@@ -131,6 +131,37 @@ int dmm_f16_fused(const void *x, int x_kind, int64_t x_ld, int64_t x_gap, const 
                   int64_t zero_count, void *workspace, size_t workspace_bytes, void *stream);
 
 /*
+ * Tensor-parallel form of dmm_f16_fused for row-parallel layers.  (No counterpart in the reference.)
+ *
+ * Every rank of a tensor-parallel group (one process per GPU) holds a K-shard of the weights and
+ * produces a partial [M, N] product that has to be summed over the ranks.  Instead of a separate
+ * all-reduce, the epilogue of this call adds its partial product to the SAME buffer on every rank:
+ * peer_out[r] (r < n_peers <= 8) are device pointers to that buffer on each rank, this rank's own
+ * included, the others mapped through NVLink peer memory (CUDA IPC / symmetric memory).  The adds
+ * are system-scope atomic adds; once every rank has run the call and dmm_xrank_barrier has
+ * completed, each rank's buffer holds its previous content plus the full product.
+ * move_src / move_dst / move_count (optional): before any of that, move_dst[i] += move_src[i] and
+ * move_src[i] = 0 on THIS rank (both local buffers) -- the residual stream changing from the buffer
+ * the previous layers read to the buffer this layer adds to, so that no rank can add into a
+ * buffer that a slower rank is still reading.  DMM_FLAG_ATOMIC | DMM_FLAG_ACCUMULATE are implied;
+ * flags: DMM_FLAG_PDL only.  Everything else as dmm_f16_fused on the small-batch tcgen05 path.
+ */
+int dmm_f16_fused_tp(const void *x, int x_kind, int64_t x_ld, int64_t x_gap, const int16_t *codes,
+                     const void *cb16, float scale, float *const *peer_out, int n_peers, int64_t M,
+                     int64_t N, int64_t K, int sign_convention, unsigned flags, float *zero_ptr,
+                     int64_t zero_count, float *move_src, float *move_dst, int64_t move_count, void *stream);
+
+/*
+ * Barrier between the ranks of a tensor-parallel group, as a kernel on `stream`: returns (on the
+ * device) once every rank has enqueued and reached the same barrier, which also makes the peer
+ * adds of the dmm_f16_fused_tp calls before it visible.  peer_flags[r] (r < world <= 8) point to
+ * an array of `world` uint32 on rank r, zero before the first barrier and owned by this function
+ * afterwards; peer_flags[rank] is this rank's own array.  The wait is bounded
+ * (DMM_STATUS_WAIT_TIMEOUT).  Every rank must call it the same number of times.
+ */
+int dmm_xrank_barrier(unsigned *const *peer_flags, int rank, int world, void *stream);
+
+/*
  * A chain of dependent products in ONE launch.  (No counterpart in the reference.)
  *
  * ops[k] is one dmm_f16_fused product, out_k += scale_k * f(x_k) . W_k^T, where op k + 1 may

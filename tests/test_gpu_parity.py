@@ -1,4 +1,6 @@
 """Parity of the CUDA path (through the C ABI) with the CPU oracle.  Needs a B200."""
+import os
+
 import numpy as np
 import pytest
 import torch
@@ -421,3 +423,55 @@ def test_linear_stack_chained_step_matches_plain():
     h_fused = stack.step(h0.clone(), fused=True)
     assert dmm.status() == 0
     assert torch.allclose(h_chain, h_fused, rtol=2e-3, atol=2e-3)
+
+
+_TP_WORKER = r"""
+import os, sys
+sys.path.insert(0, sys.argv[1])
+import torch, torch.distributed as dist
+import decode_matmul_b200 as dmm
+from decode_matmul_b200.linear import LinearStack
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+cfg = dict(hidden=1024, kv_heads=2, head_dim=64, ffn=2048, layers=3)
+cb = dmm.synthetic_codebook(42)
+ok = True
+for B in (1, 5):
+    stack = LinearStack(cfg, cb, f"cuda:{rank}", world=world, rank=rank, seed=9, scale=2.0 ** -8)
+    torch.manual_seed(1)
+    h0 = torch.randn(B, cfg["hidden"], device=f"cuda:{rank}")
+    dist.broadcast(h0, 0)
+    peer = stack._peer_state(B)
+    outs = [stack.step(h0.clone(), fused=True) for _ in range(3)]
+    os.environ["DMM_TP_PEER"] = "0"
+    ref = LinearStack(cfg, cb, f"cuda:{rank}", world=world, rank=rank, seed=9, scale=2.0 ** -8).step(h0.clone(), fused=True)
+    os.environ["DMM_TP_PEER"] = "1"
+    torch.cuda.synchronize()
+    err = max(float((o - ref).abs().max()) for o in outs)
+    ok = ok and peer is not None and err <= 2e-3 * max(1.0, float(ref.abs().max())) and dmm.status() == 0
+    print(f"rank {rank} B={B} peer={peer is not None} err={err:.3e}", flush=True)
+dist.barrier(); torch.cuda.synchronize()
+print("TP_OK" if ok else "TP_FAIL", flush=True)
+os._exit(0 if ok else 1)
+"""
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_tensor_parallel_peer_memory_step_matches_nccl(tmp_path):
+    """Two ranks (one process per GPU): the fused step whose row-parallel kernels add into every
+    rank's residual buffer over peer memory, ordered by the barrier kernel, against the same step
+    summed with NCCL all-reduce.  NVLS is off (a rank that died while bound to a multicast object
+    has faulted its peers on shared hosts)."""
+    import subprocess
+    import sys
+
+    script = tmp_path / "tp_worker.py"
+    script.write_text(_TP_WORKER)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    res = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                          "--master-addr", "127.0.0.1", "--master-port", "29533", str(script), root],
+                         capture_output=True, text=True, timeout=600, env=env)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
+    assert res.stdout.count("TP_OK") == 2

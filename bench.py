@@ -114,7 +114,7 @@ class ClockSampler:
 
 
 # ------------------------------------------------------------------------------------------
-# CPU baseline: the reference's path as BASELINE.md defines it (table-gather decode, then an
+# CPU baseline: the reference's own CPU path (its test script's table-gather decode, then an
 # fp32 torch.matmul), timed on the host cores on a bounded sample: one transformer block.
 # ------------------------------------------------------------------------------------------
 def cpu_reference_sample(batch, reps=1):

@@ -419,7 +419,8 @@ __global__ void __launch_bounds__(128) planes_kernel(const void *x, int x_mode, 
 // (K/32 k-tiles x 32 uint32), outer dimension = strips; box = kC k-tiles x 16 strips.
 // kChain == false is the plain single-product kernel: the op loops below run once with every
 // per-op value a compile-time-known kernel parameter.
-template <class Pol, int NMMA, bool kChain>
+// kTp == true adds the tensor-parallel pieces (adds into every rank's buffer, residual move).
+template <class Pol, int NMMA, bool kChain, bool kTp = false>
 __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const __grid_constant__ UmmaChainT<kChain ? kMaxOps : 1> ch) {
     using Plan = UmmaPlan<Pol, NMMA>;
     constexpr int C = Pol::kC, G = Pol::kG, NA = Pol::kNA, RING = Pol::kRing, NACC = Plan::kNAcc, NB = Plan::kNB;
@@ -672,7 +673,7 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const __grid_constan
                 const int ptid = q * 128 + trow;
                 if (p.atomic_reduce) {
                     if (n < p.N) {
-                        if (p.n_peers > 0) {
+                        if (kTp && p.n_peers > 0) {
                             // the same element on every rank: system-scope adds over NVLink peer memory
                             for (int r = 0; r < p.n_peers; ++r) {
 #pragma unroll
@@ -951,7 +952,7 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const __grid_constan
                  i += static_cast<long long>(gridDim.x) * ZT)
                 p.zero_ptr[i] = 0.f;
         }
-        if (p.move_count > 0) {
+        if (kTp && p.move_count > 0) {
             constexpr int ZT = kULoadWarps * 32;
             for (long long i = static_cast<long long>(cta) * ZT + wl * 32 + lane; i < p.move_count;
                  i += static_cast<long long>(gridDim.x) * ZT) {
@@ -1154,7 +1155,10 @@ inline int launch_umma_ops(const UmmaParams *ops, int n_ops, unsigned *sync, int
 template <class Pol, int NMMA, bool kChain>
 inline int launch_umma_ops(const UmmaParams *ops, int n_ops, unsigned *sync, int num_sms, bool pdl, cudaStream_t stream) {
     using Plan = UmmaPlan<Pol, NMMA>;
-    auto kernel = umma_kernel<Pol, NMMA, kChain>;
+    auto kernel = umma_kernel<Pol, NMMA, kChain, false>;
+    if constexpr (Pol::kIsF8 && !kChain) {  // tensor-parallel epilogue: its own instantiation, nothing of it in the plain kernel
+        if (ops[0].n_peers > 0 || ops[0].move_count > 0) kernel = umma_kernel<Pol, NMMA, kChain, true>;
+    }
     cudaError_t err =
         cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Plan::kDynBytes));
     if (err != cudaSuccess) return err;

@@ -38,7 +38,9 @@ def load_reference(ref_root):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py <path of a checkout of nalzok/decode-matmul>")
+    ref_root = sys.argv[1]
     out = os.path.dirname(os.path.abspath(__file__))
     ref = load_reference(ref_root)
     torch.random.manual_seed(42)

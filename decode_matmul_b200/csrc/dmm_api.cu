@@ -245,6 +245,48 @@ static int run_umma(bool f8, const void *x, int x_kind, long long x_ld, long lon
     return 0;
 }
 
+// Integer family on the tcgen05 kernel: one launch per chunk of 32 batch rows.
+static int run_umma_i8(const void *x, const void *codes, const void *cb64, int32_t *out, long long M, long long N,
+                       long long K, int sign_convention, unsigned flags, void *workspace, size_t workspace_bytes,
+                       cudaStream_t stream) {
+    DeviceState *d = nullptr;
+    int rc = current_device_state(&d);
+    if (rc) return rc;
+    void *ws = nullptr;
+    rc = resolve_workspace(d, M, N, K, workspace, workspace_bytes, stream, &ws);
+    if (rc) return rc;
+    // Integer sums do not depend on their order, so partial super-tiles are always added with
+    // atomics (no workspace round trip, no ticket); a plain product clears the output first.
+    if (!(flags & DMM_FLAG_ACCUMULATE)) {
+        const cudaError_t err = cudaMemsetAsync(out, 0, static_cast<size_t>(M) * static_cast<size_t>(N) * sizeof(int32_t), stream);
+        if (err != cudaSuccess) return err;
+    }
+    for (long long m0 = 0; m0 < M; m0 += 32) {
+        UmmaParams p = {};
+        p.x = reinterpret_cast<const int8_t *>(x) + static_cast<size_t>(m0) * K;
+        p.x_ld = K;
+        p.codes = codes;
+        p.cb = cb64;
+        p.out = reinterpret_cast<float *>(out + static_cast<size_t>(m0) * N);  // int32 behind the kernel's generic pointer
+        p.tickets = reinterpret_cast<unsigned *>(ws);
+        p.partials = reinterpret_cast<float *>(reinterpret_cast<uint8_t *>(ws) + ticket_bytes(N));
+        p.M = M - m0 < 32 ? M - m0 : 32;
+        p.N = N;
+        p.K = K;
+        p.scale = 1.0f;
+        p.accumulate = 1;
+        p.atomic_reduce = 1;
+        p.sign_convention = sign_convention;
+#ifdef DMM_TRACE
+        p.trace = g_trace;
+#endif
+        rc = launch_umma_i8(p, d->num_sms, (flags & DMM_FLAG_PDL) != 0, stream);
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+        if (rc) return rc;
+    }
+    return 0;
+}
+
 // ---------------------------------------------------------------------------------------
 // Fixed scratch for dmm_f16_noalloc: ticket counters, then stream-K partials for up to
 // kNoAllocMaxCtas CTAs of the fp8-operand tcgen05 kernel (2 slots x 2048 floats each).
@@ -295,8 +337,8 @@ int dmm_i8(const int8_t *x, const int16_t *codes, const int64_t *cb64, int32_t *
         rc = retile_fast(d, codes, N, K, static_cast<cudaStream_t>(stream), &tiled);
         if (rc) return rc;
     }
-    return run_stream(0, x, tiled, cb64, 0, 1.0f, out, M, N, K, sign_convention, flags, workspace, workspace_bytes,
-                      static_cast<cudaStream_t>(stream));
+    return run_umma_i8(x, tiled, cb64, out, M, N, K, sign_convention, flags, workspace, workspace_bytes,
+                       static_cast<cudaStream_t>(stream));
 }
 
 int dmm_f16_fused(const void *x, int x_kind, int64_t x_ld, int64_t x_gap, const int16_t *codes, const void *cb16,

@@ -122,8 +122,17 @@ __device__ __forceinline__ void mma_ts_f8(uint32_t d, uint32_t a, uint64_t bdesc
         : "memory");
 }
 // The same with the descriptor as two 32-bit words (only the low word changes from tile to tile).
+template <bool kInt = false>
 __device__ __forceinline__ void mma_ts_f8_lh(uint32_t d, uint32_t a, uint32_t desc_lo, uint32_t desc_hi, uint32_t idesc,
                                              uint32_t acc) {
+    if constexpr (kInt) {
+        asm volatile(
+            "{\n.reg .pred p;\n.reg .b64 bd;\nsetp.ne.b32 p, %5, 0;\nmov.b64 bd, {%2, %3};\n"
+            "tcgen05.mma.cta_group::1.kind::i8 [%0], [%1], bd, %4, p;\n}\n" ::"r"(d),
+            "r"(a), "r"(desc_lo), "r"(desc_hi), "r"(idesc), "r"(acc)
+            : "memory");
+        return;
+    }
     asm volatile(
         "{\n.reg .pred p;\n.reg .b64 bd;\nsetp.ne.b32 p, %5, 0;\nmov.b64 bd, {%2, %3};\n"
         "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%1], bd, %4, p;\n}\n" ::"r"(d),
@@ -161,6 +170,7 @@ __device__ __forceinline__ void sts64(uint32_t addr, uint32_t a, uint32_t b) {
 // kNA group buffers per decoder group in TMEM;  kC k-tiles per TMA chunk (multiple of kG).
 struct PolF8 {
     static constexpr int kIsF8 = 1;
+    static constexpr int kIsInt = 0;
     static constexpr int kFmt = kFmtFp6;
     static constexpr int kG = 2;
     static constexpr int kNA = 2;
@@ -170,8 +180,25 @@ struct PolF8 {
     static constexpr uint32_t x_tile_bytes(int) { return 1024; }  // 2 k-halves x (4 planes x 8 rows) x 16 B
     static constexpr int out_cols(int nmma) { return nmma / 4; }    // batch columns per launch: 8 or 16
 };
+// Integer family (the reference's own operator: int8 activations, int32 result, exact): the
+// structure of the fp8 policy -- epoch-resident activations, four accumulator sets -- with the
+// weights as two's-complement bytes straight from the table XOR, the int8 activations copied as
+// they are (one "plane", the batch rows are the MMA columns) and kind::i8 MMAs into int32.
+struct PolI8 {
+    static constexpr int kIsF8 = 1;
+    static constexpr int kIsInt = 1;
+    static constexpr int kFmt = kFmtTwos;
+    static constexpr int kG = 2;
+    static constexpr int kNA = 2;
+    static constexpr int kC = 4;
+    static constexpr int kRing = 3;
+    static constexpr int kACols = 8;   // 32 k x 1 byte
+    static constexpr uint32_t x_tile_bytes(int) { return 1024; }
+    static constexpr int out_cols(int nmma) { return nmma; }       // batch columns per launch
+};
 struct PolF16 {
     static constexpr int kIsF8 = 0;
+    static constexpr int kIsInt = 0;
     static constexpr int kFmt = kFmtOffset;
     static constexpr int kG = 1;
     static constexpr int kNA = 2;
@@ -198,8 +225,9 @@ __host__ __device__ inline int first_epoch_tiles(int E, int M) {
 // Bytes of the E5M2 planes of one k-tile: [k-half][plane][row][16 B].  Up to 8 batch rows the
 // rows of a plane are packed densely (M rows); the 64- and 128-column variants pad a plane to 16
 // and 32 rows.
-template <int NMMA>
+template <int NMMA, bool kInt = false>
 __host__ __device__ inline uint32_t plane_tile_bytes(int M) {
+    if (kInt) return 32u * static_cast<uint32_t>(NMMA);  // int8: [k-half][row < NMMA][16 B], rows padded to the MMA width
     return 128u * static_cast<uint32_t>(NMMA > 64 ? 32 : (NMMA > 32 ? 16 : M));
 }
 
@@ -290,6 +318,15 @@ struct UmmaParams {
     unsigned dyn_smem_bytes;
     long long *trace;    // debugging aid (builds with -DDMM_TRACE only): clock stamps of CTA 0
 };
+
+// Accumulator element of the epilogue: fp32, or int32 for the integer family.
+template <bool kInt> struct AccType { using type = float; };
+template <> struct AccType<true> { using type = int; };
+template <class Acc> __device__ __forceinline__ Acc acc_from_bits(uint32_t r);
+template <> __device__ __forceinline__ float acc_from_bits<float>(uint32_t r) { return __uint_as_float(r); }
+template <> __device__ __forceinline__ int acc_from_bits<int>(uint32_t r) { return static_cast<int>(r); }
+__device__ __forceinline__ float acc_scaled(float scale, float v) { return scale * v; }
+__device__ __forceinline__ int acc_scaled(float, int v) { return v; }
 
 // Several dependent products in one launch ("chain"): op k+1 reads what op k wrote.  The CTAs
 // stay resident; between two ops only the activation loaders wait (for every CTA to have
@@ -441,7 +478,8 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const __grid_constan
     if (tid == 0) DMM_STAMP(0, 0, 0);
     const UmmaParams &p0 = ch.op[0];  // codebook, sign convention, batch and input kind are common to all ops
     const int n_ops = kChain ? ch.n_ops : 1;
-    const uint4 cb_pre = lut_prefetch(p0.cb, tid);  // the codebook is static data: fetch it first
+    // the codebook is static data: fetch it first (fp16 table; the integer family's int64 table is read in lut_fill)
+    const uint4 cb_pre = Pol::kIsInt ? make_uint4(0, 0, 0, 0) : lut_prefetch(p0.cb, tid);
 
     if (ring_addr + Plan::kRingBytes > base + p0.dyn_smem_bytes) {  // uniform over the grid
         if (tid == 0) raise_status(DMM_STATUS_BAD_SMEM);
@@ -480,7 +518,8 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const __grid_constan
     bool bad_cb = false;
     if (warp < kUDecWarps) {
         if (tid == 0) DMM_STAMP(0, 1, 0);
-        bad_cb = lut_fill(lut_addr, p0.cb, 1, p0.sign_convention, Pol::kFmt, tid, kUDecWarps * 32, Pol::kIsF8 != 0, &cb_pre);
+        bad_cb = lut_fill(lut_addr, p0.cb, Pol::kIsInt ? 0 : 1, p0.sign_convention, Pol::kFmt, tid, kUDecWarps * 32,
+                          Pol::kIsF8 != 0 && !Pol::kIsInt, Pol::kIsInt ? nullptr : &cb_pre);
         if (tid == 0) DMM_STAMP(0, 1, 1);
         if (lane == 0) DMM_STAMP(0, 8 + warp, 0);
         named_barrier(4, kUThreads);
@@ -531,7 +570,7 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const __grid_constan
         const int q = warp >> 2, wq = warp & 3;
         const uint32_t gring = ring_addr + static_cast<uint32_t>(q) * (RING * Plan::kSlotBytes);  // ring of group q
         if (bad_cb) raise_status(DMM_STATUS_BAD_CODEBOOK);
-        const LutLane ll = lut_lane(lut_addr, lane, Pol::kIsF8 != 0);
+        const LutLane ll = lut_lane(lut_addr, lane, Pol::kIsF8 != 0 && !Pol::kIsInt);
         if (tid == 0) DMM_STAMP(0, 0, 2);
 
         const uint32_t tlane = tmem + (static_cast<uint32_t>(wq * 32) << 16);
@@ -575,7 +614,14 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const __grid_constan
                             const uint32_t w[4] = {cw.x, cw.y, cw.z, cw.w};
 #pragma unroll
                             for (int t = 0; t < 4; ++t) {
-                                const uint2 d0 = decode8_fp6<0>(w[t], ll), d1 = decode8_fp6<1>(w[t], ll);
+                                uint2 d0, d1;
+                                if constexpr (Pol::kIsInt) {
+                                    d0 = decode8<0>(w[t], ll);
+                                    d1 = decode8<1>(w[t], ll);
+                                } else {
+                                    d0 = decode8_fp6<0>(w[t], ll);
+                                    d1 = decode8_fp6<1>(w[t], ll);
+                                }
                                 r0[8 * i + 2 * t] = d0.x; r0[8 * i + 2 * t + 1] = d0.y;
                                 r1[8 * i + 2 * t] = d1.x; r1[8 * i + 2 * t + 1] = d1.y;
                             }
@@ -625,10 +671,14 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const __grid_constan
                 mbar_wait(bar(Plan::kBarDReady), static_cast<uint32_t>(segidx & 1), flags);
                 tc_fence_after();
                 if (tid == 0) DMM_STAMP(4, segidx, 1);
-                float v[NB];
+                // the accumulators are fp32, or int32 for the integer family (exact, no scale)
+                using Acc = typename AccType<Pol::kIsInt != 0>::type;
+                Acc v[NB];
 #pragma unroll
-                for (int b = 0; b < NB; ++b) v[b] = 0.f;
-                if (Pol::kIsF8 && p.M == 1) {
+                for (int b = 0; b < NB; ++b) v[b] = Acc(0);
+                Acc *const out_acc = reinterpret_cast<Acc *>(p.out);
+                Acc *const partials_acc = reinterpret_cast<Acc *>(p.partials);
+                if (Pol::kIsF8 && !Pol::kIsInt && p.M == 1) {
                     // batch 1: only column 8 * plane of every accumulator carries data; fetch those
                     // sixteen words with one wait instead of whole accumulators one after the other
                     uint32_t r[16];
@@ -643,7 +693,7 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const __grid_constan
                     }
                     tmem_wait_ld(r);
 #pragma unroll
-                    for (int e = 0; e < 16; ++e) v[0] += __uint_as_float(r[e]);
+                    for (int e = 0; e < 16; ++e) v[0] += acc_from_bits<Acc>(r[e]);
                 } else {
 #pragma unroll
                     for (int a = 0; a < NACC; ++a) {
@@ -655,7 +705,7 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const __grid_constan
                                 tmem_wait_ld(r);
                                 // PolF8: column 8*plane + b; PolF16: column b
 #pragma unroll
-                                for (int e = 0; e < 16; ++e) v[(b0 + e) % NB] += __uint_as_float(r[e]);
+                                for (int e = 0; e < 16; ++e) v[(b0 + e) % NB] += acc_from_bits<Acc>(r[e]);
                             }
                         }
                     }
@@ -678,12 +728,12 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const __grid_constan
                             for (int r = 0; r < p.n_peers; ++r) {
 #pragma unroll
                                 for (int b = 0; b < NB; ++b)
-                                    if (b < p.M) atomicAdd_system(p.peer_out[r] + b * p.N + n, p.scale * v[b]);
+                                    if (b < p.M) atomicAdd_system(reinterpret_cast<Acc *>(p.peer_out[r]) + b * p.N + n, acc_scaled(p.scale, v[b]));
                             }
                         } else {
 #pragma unroll
                             for (int b = 0; b < NB; ++b)
-                                if (b < p.M) atomicAdd(p.out + b * p.N + n, p.scale * v[b]);
+                                if (b < p.M) atomicAdd(out_acc + b * p.N + n, acc_scaled(p.scale, v[b]));
                         }
                     }
                 } else if (full) {
@@ -691,13 +741,13 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const __grid_constan
 #pragma unroll
                         for (int b = 0; b < NB; ++b)
                             if (b < p.M) {
-                                float *o = p.out + b * p.N + n;
-                                const float r = p.scale * v[b];
+                                Acc *o = out_acc + b * p.N + n;
+                                const Acc r = acc_scaled(p.scale, v[b]);
                                 *o = p.accumulate ? *o + r : r;
                             }
                     }
                 } else {
-                    float *mine = p.partials + static_cast<long long>(cta * 2 + my_slot) * Plan::kPartial + q * NB * 128 + trow;
+                    Acc *mine = partials_acc + static_cast<long long>(cta * 2 + my_slot) * Plan::kPartial + q * NB * 128 + trow;
 #pragma unroll
                     for (int b = 0; b < NB; ++b)
                         if (b < p.M) mine[b * 128] = v[b];
@@ -720,24 +770,24 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const __grid_constan
                             for (int b = 0; b < NB; ++b)
                                 if (b < p.M) {
                                     // fixed summation order; eight loads in flight at a time
-                                    float tot = 0.f;
+                                    Acc tot = Acc(0);
                                     for (int c0 = 0; c0 < ncta; c0 += 8) {
-                                        float part[8];
+                                        Acc part[8];
 #pragma unroll
                                         for (int e = 0; e < 8; ++e) {
-                                            part[e] = 0.f;
+                                            part[e] = Acc(0);
                                             if (c0 + e < ncta) {
                                                 const int c = c_lo + c0 + e;
                                                 const int slot_c = part32_begin(p.part, c) > ss_a ? 0 : 1;
-                                                part[e] = __ldcg(p.partials + static_cast<long long>(c * 2 + slot_c) * Plan::kPartial +
+                                                part[e] = __ldcg(partials_acc + static_cast<long long>(c * 2 + slot_c) * Plan::kPartial +
                                                                  (q * NB + b) * 128 + trow);
                                             }
                                         }
 #pragma unroll
                                         for (int e = 0; e < 8; ++e) tot += part[e];
                                     }
-                                    float *o = p.out + b * p.N + n;
-                                    const float r = p.scale * tot;
+                                    Acc *o = out_acc + b * p.N + n;
+                                    const Acc r = acc_scaled(p.scale, tot);
                                     *o = p.accumulate ? *o + r : r;
                                 }
                         }
@@ -781,16 +831,20 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const __grid_constan
             for (int op = 0; op < n_ops; ++op) {
             const UmmaParams &p = ch.op[op];
             DMM_OP_GEOMETRY(p);
-            const uint32_t idesc = Pol::kIsF8
+            // instruction descriptor: D fp32 (1) or int32 (2) at bit 4; A / B formats at bits 7 / 10
+            // (f8f6f4: E2M3 = 3, E5M2 = 1; i8: signed = 1); N >> 3 at 17; M >> 4 at 24
+            const uint32_t idesc = Pol::kIsInt
+                                       ? ((2u << 4) | (1u << 7) | (1u << 10) | ((NMMA >> 3) << 17) | ((128u >> 4) << 24))
+                                   : Pol::kIsF8
                                        ? ((1u << 4) | (3u << 7) | (1u << 10) | ((NMMA >> 3) << 17) | ((128u >> 4) << 24))
                                        : ((1u << 4) | ((NMMA >> 3) << 17) | ((128u >> 4) << 24));
             // descriptor of activation stage 0; later stages and k-halves only move the address field
-            const uint32_t tile_b = plane_tile_bytes<NMMA>(static_cast<int>(p.M));  // fp8: bytes of one k-tile of planes
+            const uint32_t tile_b = plane_tile_bytes<NMMA, Pol::kIsInt != 0>(static_cast<int>(p.M));  // fp8: bytes of one k-tile of planes
             const int E = epoch_tiles(Plan::kEpochBytes, tile_b);  // k-tiles per epoch
             const int E0 = first_epoch_tiles(E, static_cast<int>(p.M));           // the first one is short
             // fp8: a plane is one 8-row core matrix (rows past the batch overlap the next plane and
             // land in unused columns) or, for the 16-row layout, two of them
-            const uint64_t xdesc0 = Pol::kIsF8 ? smem_desc(x_addr, tile_b / 2, NMMA > 32 ? 128u : tile_b / 8)
+            const uint64_t xdesc0 = Pol::kIsF8 ? smem_desc(x_addr, tile_b / 2, (NMMA > 32 || Pol::kIsInt) ? 128u : tile_b / 8)
                                                : smem_desc(x_addr, NMMA * 16, 128);
             int cur_ep = -1, ep_beg = 0, ep_end = 0;  // fp8: epoch of this op being read and its k-tile range
             int ep_slot = eg_base % Plan::kEpochs;    // its buffer, the parity of that buffer's barriers
@@ -850,10 +904,10 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const __grid_constan
                                     const uint32_t acc = (first && i == 0) ? 0u : 1u;
                                     if (leader) {
                                         if constexpr (TP == 1) {
-                                            mma_ts_f8_lh(d_col0, a_col + i * Pol::kACols, xlo, xdesc_hi, idesc, acc);
-                                            mma_ts_f8_lh(d_col0 + NACC * NMMA, a_col + (G + i) * Pol::kACols, xlo, xdesc_hi, idesc, acc);
+                                            mma_ts_f8_lh<Pol::kIsInt != 0>(d_col0, a_col + i * Pol::kACols, xlo, xdesc_hi, idesc, acc);
+                                            mma_ts_f8_lh<Pol::kIsInt != 0>(d_col0 + NACC * NMMA, a_col + (G + i) * Pol::kACols, xlo, xdesc_hi, idesc, acc);
                                         } else {
-                                            mma_ts_f8_lh(d_col0, a_col + (tp * G + i) * Pol::kACols, xlo, xdesc_hi, idesc, acc);
+                                            mma_ts_f8_lh<Pol::kIsInt != 0>(d_col0, a_col + (tp * G + i) * Pol::kACols, xlo, xdesc_hi, idesc, acc);
                                         }
                                     }
                                 }
@@ -978,7 +1032,7 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const __grid_constan
             // densely packed [tile][k-half][plane][row][16 B]; the issuers point their operand
             // descriptors straight into these buffers.  A piece is 8 consecutive k of one row.
             constexpr int U = 4;  // pieces in flight per thread
-            const uint32_t tile_b = plane_tile_bytes<NMMA>(M);
+            const uint32_t tile_b = plane_tile_bytes<NMMA, Pol::kIsInt != 0>(M);
             const int E = epoch_tiles(Plan::kEpochBytes, tile_b);
             // The first epoch is short: nothing can be multiplied before it is staged, and the
             // loaders may only start once the previous kernel of the stream has finished.
@@ -1029,6 +1083,30 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const __grid_constan
                 const int nt = ntiles - t_lo < e_len ? ntiles - t_lo : e_len;
                 const int npieces = nt * ppt;
                 const uint32_t ebuf = x_addr + (eg % Plan::kEpochs) * Plan::kEpochBytes;
+                if constexpr (Pol::kIsInt) {
+                    // int8 activations go in as they are: a piece is 16 consecutive k of one row
+                    const int8_t *x8 = reinterpret_cast<const int8_t *>(p.x);
+                    const int nq = nt * 2 * M;
+                    for (int pbase = 0; pbase < nq; pbase += LT * U) {
+                        uint4 val[U];
+                        uint32_t dst[U];
+#pragma unroll
+                        for (int u = 0; u < U; ++u) {
+                            const int pc = pbase + u * LT + lt;
+                            dst[u] = 0;
+                            if (pc < nq) {
+                                const int jl = pc / (2 * M), rem = pc - jl * (2 * M), row = rem >> 1, kh = rem & 1;
+                                const int gt = i0 + t_lo + jl;
+                                const int kt = gt - (gt / KT) * KT;
+                                dst[u] = ebuf + jl * tile_b + kh * (tile_b / 2) + row * 16;
+                                val[u] = __ldcg(reinterpret_cast<const uint4 *>(x8 + static_cast<long long>(row) * p.x_ld + 32 * kt + 16 * kh));
+                            }
+                        }
+#pragma unroll
+                        for (int u = 0; u < U; ++u)
+                            if (dst[u] != 0) sts128(dst[u], val[u]);
+                    }
+                } else
                 for (int pbase = 0; pbase < npieces; pbase += LT * U) {
                     uint32_t h[U][4];
                     uint32_t dst[U];
@@ -1235,6 +1313,12 @@ inline int launch_planes(const void *x, int x_mode, long long x_ld, long long x_
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, planes_kernel, x, x_mode, x_ld, x_gap, M, K, planes_rows(M), planes);
+}
+
+// Integer family: int8 activations, up to 32 batch rows per launch, int32 result.
+inline int launch_umma_i8(const UmmaParams &p, int num_sms, bool pdl, cudaStream_t stream) {
+    if (p.M <= 16) return launch_umma_one<PolI8, 16>(p, num_sms, pdl, stream);
+    return launch_umma_one<PolI8, 32>(p, num_sms, pdl, stream);
 }
 
 // f8 != 0: PolF8 (needs M <= 32); else PolF16 with M <= 64.

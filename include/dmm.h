@@ -92,6 +92,8 @@ extern "C" {
  * (4-argument, in-place accumulate form: flags = DMM_FLAG_ACCUMULATE, DMM_SIGN_FAST,
  * DMM_LAYOUT_FAST).  Accepts every M >= 1, N % 16 == 0 (N % 32 for the fast layout),
  * K % 32 == 0; the reference's extra limits (M % 8, K % 2048, K >= 4096) are gone.
+ * Runs on the tcgen05 kernel (kind::i8 MMAs into int32 accumulators in tensor memory), 32 batch rows
+ * per pass over the weights.
  * workspace may be NULL: the library then uses a per-device buffer it allocates on first
  * use; calls that can overlap on the GPU must pass distinct workspaces.
  */

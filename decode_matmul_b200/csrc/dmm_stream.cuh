@@ -366,10 +366,9 @@ inline int launch_one(const StreamParams &p_in, int num_sms, bool pdl, cudaStrea
 }
 
 inline int launch_stream(int family, const StreamParams &p, int num_sms, bool pdl, cudaStream_t stream) {
-    if (family == 0) {
-        if (p.M <= 8) return launch_one<FamI8, 4, 1>(p, num_sms, pdl, stream);
-        return launch_one<FamI8, 2, 2>(p, num_sms, pdl, stream);
-    }
+    // The integer family runs on the tcgen05 kernel (umma_kernel<PolI8, *>); this kernel keeps its
+    // integer policy (FamI8) only as the description of that arithmetic and is no longer launched with it.
+    if (family == 0) return DMM_ERR_UNSUPPORTED;
     if (p.M <= 8) return launch_one<FamF16, 4, 1>(p, num_sms, pdl, stream);
     return launch_one<FamF16, 2, 2>(p, num_sms, pdl, stream);
 }

@@ -446,6 +446,53 @@ int dmm_xrank_barrier(unsigned *const *peer_flags, int rank, int world, void *st
     return cudaLaunchKernelEx(&cfg, xrank_barrier_kernel, bp);
 }
 
+int dmm_xrank_allreduce_add(float *dst, const float *const *peer_src, float *zero_local, int64_t count,
+                            unsigned *const *peer_flags, int rank, int world, void *stream) {
+    if (!dst || !peer_src || !peer_flags) return DMM_ERR_NULL;
+    if (world < 1 || world > 8 || rank < 0 || rank >= world) return DMM_ERR_ARG;
+    if (count < 4 || count % 4 != 0) return DMM_ERR_SHAPE;
+    if (!aligned16(dst) || (zero_local && !aligned16(zero_local))) return DMM_ERR_ALIGN;
+    DeviceState *d = nullptr;
+    int rc = current_device_state(&d);
+    if (rc) return rc;
+    {
+        std::lock_guard<std::mutex> lock(g_mutex);
+        if (d->xrank_counter == nullptr) {
+            cudaError_t err = cudaMalloc(reinterpret_cast<void **>(&d->xrank_counter), 256);
+            if (err != cudaSuccess) return err;
+            err = cudaMemset(d->xrank_counter, 0, 256);
+            if (err != cudaSuccess) return err;
+        }
+    }
+    XrankAllreduceParams ap = {};
+    for (int r = 0; r < world; ++r) {
+        if (!peer_src[r] || !peer_flags[r]) return DMM_ERR_NULL;
+        if (!aligned16(peer_src[r])) return DMM_ERR_ALIGN;
+        ap.peer_src[r] = peer_src[r];
+        ap.flags[r] = peer_flags[r];
+    }
+    ap.counter = d->xrank_counter;       // word 0: barriers / all-reduces done; word 16: block ticket
+    ap.ticket = d->xrank_counter + 16;
+    ap.dst = dst;
+    ap.zero_local = zero_local;
+    ap.count = count;
+    ap.rank = rank;
+    ap.world = world;
+    long long blocks = (count / 4 + 255) / 256;
+    if (blocks > 16) blocks = 16;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(blocks));
+    cfg.blockDim = dim3(256);
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return cudaLaunchKernelEx(&cfg, xrank_allreduce_kernel, ap);
+}
+
 int dmm_f16_chain(const dmm_chain_op *ops, int n_ops, const void *cb16, int64_t M, int sign_convention,
                   unsigned flags, void *stream) {
     if (!ops || !cb16) return DMM_ERR_NULL;

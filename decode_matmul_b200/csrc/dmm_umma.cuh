@@ -429,6 +429,86 @@ __global__ void __launch_bounds__(32) xrank_barrier_kernel(const XrankBarrierPar
     __threadfence_system();
 }
 
+// One-shot all-reduce-and-add for the tensor-parallel step: every rank has accumulated its partial
+// [count] fp32 product into its own `src` buffer (peer_src[r] = that buffer on rank r, mapped
+// through peer memory); this kernel waits until all ranks have got that far (the barrier of
+// xrank_barrier_kernel, signalled by block 0, awaited by every block on this rank's own flag words),
+// then each rank PULLS the partials of all ranks with coalesced 16-byte loads over NVLink, adds them
+// in rank order (so every rank computes the same bits) and adds the sum to its local `dst`.  It also
+// clears `zero_local`, the partial buffer of the layer before: all ranks have finished reading it
+// once they have signalled this barrier.  The barrier number is the device counter + 1, read by every
+// block before the last block to finish increments it.
+struct XrankAllreduceParams {
+    const float *peer_src[8];
+    unsigned *flags[8];
+    unsigned *counter;   // this rank's count of finished all-reduces (local)
+    unsigned *ticket;    // this rank's count of finished blocks of the running kernel (local, zero between kernels)
+    float *dst;          // local
+    float *zero_local;   // local, may be null
+    long long count;     // floats, multiple of 4
+    int rank, world;
+};
+__global__ void __launch_bounds__(256) xrank_allreduce_kernel(const XrankAllreduceParams ap) {
+    grid_dep_launch();
+    grid_dep_wait();
+    __shared__ int failed;
+    const int t = threadIdx.x;
+    if (t == 0) failed = 0;
+    const unsigned e = *reinterpret_cast<volatile const unsigned *>(ap.counter) + 1u;
+    __syncthreads();
+    if (blockIdx.x == 0 && t < ap.world) {
+        __threadfence_system();
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(ap.flags[t] + ap.rank), "r"(e) : "memory");
+    }
+    if (t < ap.world) {
+        const unsigned *mine = ap.flags[ap.rank] + t;
+        const long long t0 = clock64();
+        for (;;) {
+            unsigned v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+            if (static_cast<int>(v - e) >= 0) break;
+            if (clock64() - t0 > kWaitLimitCycles) {
+                raise_status(DMM_STATUS_WAIT_TIMEOUT);
+                failed = 1;
+                break;
+            }
+            __nanosleep(100);
+        }
+    }
+    __syncthreads();
+    if (!failed) {
+        const long long n4 = ap.count / 4;
+        for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + t; i < n4;
+             i += static_cast<long long>(gridDim.x) * blockDim.x) {
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int r = 0; r < ap.world; ++r) {
+                float4 v;
+                asm volatile("ld.relaxed.sys.global.v4.f32 {%0,%1,%2,%3}, [%4];"
+                             : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+                             : "l"(reinterpret_cast<const float4 *>(ap.peer_src[r]) + i)
+                             : "memory");
+                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+            }
+            float4 *d = reinterpret_cast<float4 *>(ap.dst) + i;
+            float4 o = *d;
+            o.x += acc.x; o.y += acc.y; o.z += acc.z; o.w += acc.w;
+            *d = o;
+            if (ap.zero_local != nullptr) reinterpret_cast<float4 *>(ap.zero_local)[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
+    // the last block to finish moves the counter on (every block has read it by then)
+    __threadfence();
+    __syncthreads();
+    if (t == 0) {
+        const unsigned done = atomicAdd(ap.ticket, 1u);
+        if (done == gridDim.x - 1) {
+            *ap.ticket = 0;
+            __threadfence();
+            atomicAdd(ap.counter, 1u);
+        }
+    }
+}
+
 // Splits the activations of one call into E5M2 planes ONCE, in the layout the tcgen05 kernel's
 // epoch buffers use: [k-tile][k-half][plane][row < rows_padded][16 B].  With more than a few
 // batch rows the per-CTA split inside umma_kernel (every CTA repeats it for its k range) costs

@@ -157,7 +157,7 @@ class LinearStack:
             flags.zero_()
             h_res, h_flags = symm.rendezvous(res, group), symm.rendezvous(flags, group)
             nbytes = batch * self.hidden * 4
-            peer = dict(res=res, flags=flags, cur=0,
+            peer = dict(res=res, flags=flags, cur=0, mode=os.environ.get("DMM_TP_MODE", "pull"),
                         res_ptrs=[[int(ptr) + i * nbytes for ptr in h_res.buffer_ptrs] for i in range(2)],
                         flag_ptrs=[int(ptr) for ptr in h_flags.buffer_ptrs])
             ok.fill_(1)
@@ -202,13 +202,51 @@ class LinearStack:
         res[cur].zero_()  # restores the starting state: both buffers zero, so `cur` may restart at 0
         return h
 
+    def _step_fused_pull(self, h: torch.Tensor, peer) -> torch.Tensor:
+        """Tensor-parallel fused step with a one-shot all-reduce kernel: a row-parallel layer
+        accumulates its partial product into this rank's own symmetric buffer, then one kernel waits
+        for all ranks, pulls every rank's partial over NVLink and adds the sum to the local residual.
+        Two partial buffers alternate; the all-reduce of one layer clears the buffer of the layer
+        before (all ranks have finished reading it by then), so one barrier per layer is enough."""
+        import os
+
+        from .ops import decode_matmul_fused as mm
+        from .ops import xrank_allreduce_add
+
+        B = h.shape[0]
+        buf = self._buffers(B)
+        a, g = buf["a"], buf["g"]
+        ffn_loc = self.ffn // self.world
+        part, cur = peer["res"], peer["cur"]
+        a.zero_()
+        kw = dict(accumulate=True, atomic=True, pdl=True)
+        for blk in self.layers:
+            q, o, gu, dn = blk["qkv"], blk["o"], blk["gate_up"], blk["down"]
+            mm(h, q.codes, q.codebook, q.scale, a, x_kind=_lib.X_F32, zero=g, **kw)
+            mm(a, o.codes, o.codebook, o.scale, part[cur], x_kind=_lib.X_F32, **kw)
+            xrank_allreduce_add(h, peer["res_ptrs"][cur], peer["flag_ptrs"], self.rank, zero=part[1 - cur])
+            cur = 1 - cur
+            mm(h, gu.codes, gu.codebook, gu.scale, g, x_kind=_lib.X_F32, zero=a, **kw)
+            mm(g, dn.codes, dn.codebook, dn.scale, part[cur], x_kind=_lib.X_F32_SILU_MUL, x_gap=ffn_loc, **kw)
+            xrank_allreduce_add(h, peer["res_ptrs"][cur], peer["flag_ptrs"], self.rank, zero=part[1 - cur])
+            cur = 1 - cur
+        peer["cur"] = cur  # an even number of row-parallel layers brings it back to where it started
+        return h
+
     def _step_fused(self, h: torch.Tensor) -> torch.Tensor:
         from .ops import decode_matmul_fused as mm
 
         if self.world > 1 and h.shape[0] <= 32:
+            import os
+
             peer = self._peer_state(h.shape[0])
             if peer is not None:
-                return self._step_fused_peer(h, peer)
+                # measured on B200 (ms per step at batch 1): pull 5.36 / 4.84 / 5.63 and push 5.67 / - / 5.37
+                # at 2 / 4 / 8 ranks
+                mode = os.environ.get("DMM_TP_MODE", "pull" if self.world <= 4 else "push")
+                if mode == "push":
+                    return self._step_fused_peer(h, peer)
+                return self._step_fused_pull(h, peer)
 
         buf = self._buffers(h.shape[0])
         a, g, po, pd = buf["a"], buf["g"], buf["po"], buf["pd"]

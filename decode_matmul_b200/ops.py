@@ -166,6 +166,22 @@ def xrank_barrier(peer_flag_ptrs, rank, device):
     _lib.check(rc, "xrank_barrier")
 
 
+def xrank_allreduce_add(dst, peer_src_ptrs, peer_flag_ptrs, rank, *, zero=None):
+    """``dst += sum over ranks of the buffers at peer_src_ptrs`` as one kernel that first waits for all
+    ranks (``dmm_xrank_allreduce_add``); ``zero``: local fp32 tensor cleared as well."""
+    _check_input(dst, "dst", torch.float32)
+    if zero is not None:
+        _check_input(zero, "zero", torch.float32)
+        _req(zero.numel() == dst.numel(), "zero and dst differ in size")
+    world = len(peer_src_ptrs)
+    src = (ctypes.c_void_p * world)(*[int(v) for v in peer_src_ptrs])
+    flg = (ctypes.c_void_p * world)(*[int(v) for v in peer_flag_ptrs])
+    with torch.cuda.device(dst.device):
+        rc = _lib.lib().dmm_xrank_allreduce_add(_ptr(dst), src, None if zero is None else _ptr(zero), dst.numel(), flg,
+                                                rank, world, _stream_ptr(dst.device))
+    _lib.check(rc, "xrank_allreduce_add")
+
+
 def decode_matmul_chain(ops, codebook_fp16, *, sign_convention=_lib.SIGN_SLOW, pdl=False):
     """Up to ``CHAIN_MAX_OPS`` dependent products in one launch (``dmm_f16_chain``).
 

@@ -164,6 +164,21 @@ int dmm_f16_fused_tp(const void *x, int x_kind, int64_t x_ld, int64_t x_gap, con
 int dmm_xrank_barrier(unsigned *const *peer_flags, int rank, int world, void *stream);
 
 /*
+ * One-shot all-reduce-and-add between the ranks of a tensor-parallel group, as a kernel on `stream`:
+ * dst[i] += sum over ranks r of peer_src[r][i], i < count (count % 4 == 0), where peer_src[r] is the
+ * buffer on rank r into which that rank's row-parallel layer accumulated its partial product
+ * (plain dmm_f16_fused with DMM_FLAG_ATOMIC; this rank's own buffer included, the others mapped through
+ * peer memory).  The kernel first runs the barrier of dmm_xrank_barrier (same peer_flags, same
+ * rules; do not mix the two on one set of flags), then pulls the partials with coalesced loads over
+ * NVLink and adds them in rank order, so every rank obtains the same bits.  zero_local (optional):
+ * a local buffer of `count` floats that is cleared as well -- the partial buffer of the row-parallel
+ * layer BEFORE this one, which every rank has finished reading once it has reached this barrier;
+ * alternating two partial buffers this way needs no second barrier.
+ */
+int dmm_xrank_allreduce_add(float *dst, const float *const *peer_src, float *zero_local, int64_t count,
+                            unsigned *const *peer_flags, int rank, int world, void *stream);
+
+/*
  * A chain of dependent products in ONE launch.  (No counterpart in the reference.)
  *
  * ops[k] is one dmm_f16_fused product, out_k += scale_k * f(x_k) . W_k^T, where op k + 1 may

@@ -443,7 +443,11 @@ for B in (1, 5):
     h0 = torch.randn(B, cfg["hidden"], device=f"cuda:{rank}")
     dist.broadcast(h0, 0)
     peer = stack._peer_state(B)
-    outs = [stack.step(h0.clone(), fused=True) for _ in range(3)]
+    outs = [stack.step(h0.clone(), fused=True) for _ in range(3)]          # one-shot all-reduce kernel (default)
+    os.environ["DMM_TP_MODE"] = "push"
+    push = LinearStack(cfg, cb, f"cuda:{rank}", world=world, rank=rank, seed=9, scale=2.0 ** -8)
+    outs += [push.step(h0.clone(), fused=True) for _ in range(3)]          # adds into every rank's buffer from the epilogue
+    os.environ["DMM_TP_MODE"] = "pull"
     os.environ["DMM_TP_PEER"] = "0"
     ref = LinearStack(cfg, cb, f"cuda:{rank}", world=world, rank=rank, seed=9, scale=2.0 ** -8).step(h0.clone(), fused=True)
     os.environ["DMM_TP_PEER"] = "1"
@@ -459,9 +463,9 @@ os._exit(0 if ok else 1)
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_tensor_parallel_peer_memory_step_matches_nccl(tmp_path):
-    """Two ranks (one process per GPU): the fused step whose row-parallel kernels add into every
-    rank's residual buffer over peer memory, ordered by the barrier kernel, against the same step
-    summed with NCCL all-reduce.  NVLS is off (a rank that died while bound to a multicast object
+    """Two ranks (one process per GPU): the fused step summed over the ranks by the one-shot
+    all-reduce kernel (partials pulled over peer memory) and by epilogues that add into every rank's
+    residual buffer, both against the same step summed with NCCL all-reduce.  NVLS is off (a rank that died while bound to a multicast object
     has faulted its peers on shared hosts)."""
     import subprocess
     import sys

@@ -1,21 +1,26 @@
-// tcgen05 decode-matmul kernel (fp16 family, every batch size).
+// tcgen05 decode-matmul kernel (both families, every batch size) and its small companions.
 //
 // The decoded weights are the A operand of tcgen05.mma and never touch shared memory: each
-// decoder thread owns one output row, decodes that row's codes in registers and writes
-// them into tensor memory with tcgen05.st; the activations are the B operand, staged in
-// shared memory in the canonical no-swizzle K-major layout; accumulators live in TMEM.
+// decoder thread owns two output rows, decodes their codes in registers and writes them into
+// tensor memory with tcgen05.st; the activations are the B operand, staged in shared memory in
+// the canonical no-swizzle K-major layout; accumulators live in TMEM.
 //
-// Two operand policies share the kernel:
-//   PolF8   (batch <= 8)  weights as fp6 E2M3 bytes (sign << 5 | |q|, value q/8: exact, and
-//                         produced by the table XOR alone, 7 instructions per code), the
-//                         fp16 activations split EXACTLY into four E5M2 planes (the top byte
-//                         of the half, then of the remainder, ...), kind::f8f6f4, K = 32.
-//                         The four planes are stacked along the MMA n dimension (n = 8*plane
-//                         + batch column, N = 32), so one MMA per k-tile does all of them and
-//                         the epilogue adds the four column groups.  The decode, the actual
-//                         limiter of a 2-bit-per-weight stream, is at its minimum.
-//   PolF16  (batch >= 9)  weights as fp16 integers q (byte -> half by magic number),
-//                         activations as fp16, kind::f16, K = 16.
+// Operand policies that share the kernel:
+//   PolF8   fp16 family, what the library picks.  Weights as fp6 E2M3 bytes (sign << 5 | |q|,
+//           value q/8: exact, and produced by the table XOR alone, 7 instructions per code),
+//           the fp16 activations split EXACTLY into four E5M2 planes (the top byte of the half,
+//           then of the remainder, ...), kind::f8f6f4, K = 32.  The planes are stacked along
+//           the MMA n dimension (N = 32 / 64 / 128 columns for up to 8 / 16 / 32 batch rows), so
+//           one MMA per k-tile does all of them and the epilogue adds the four column groups.
+//           Up to 3 batch rows the loader warps split the activations themselves; from 4 rows
+//           on planes_kernel splits them once per call and the loaders only issue bulk copies.
+//   PolI8   integer family (the reference's operator).  Weights as two's-complement bytes,
+//           int8 activations as they are, kind::i8 into int32 accumulators, N = 16 / 32.
+//   PolF16  fp16 family, fp16 operands (DMM_PATH_TCGEN05): weights as fp16 integers q (byte ->
+//           half by magic number), activations as fp16, kind::f16, K = 16.  A cross-check.
+// Template flags: kChain (several dependent products in one cooperative launch, the CTAs stay
+// resident) and kTp (tensor-parallel epilogue that adds into every rank's buffer).
+// Companions in this file: planes_kernel, xrank_barrier_kernel, xrank_allreduce_kernel.
 //
 // Work decomposition.  A super-tile is 16 strips = 256 output rows = two M=128 MMA tiles:
 // tile 0 holds strip rows 0..7 (h = 0) and tile 1 strip rows 8..15 (h = 1) of the 16 strips,

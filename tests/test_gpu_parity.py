@@ -465,7 +465,7 @@ os._exit(0 if ok else 1)
 def test_tensor_parallel_peer_memory_step_matches_nccl(tmp_path):
     """Two ranks (one process per GPU): the fused step summed over the ranks by the one-shot
     all-reduce kernel (partials pulled over peer memory) and by epilogues that add into every rank's
-    residual buffer, both against the same step summed with NCCL all-reduce.  NVLS is off (a rank that died while bound to a multicast object
+    residual buffer, both against the same step summed with NCCL all-reduce.  NVLS is off (a rank that died while its memory was bound to an NVLink group object
     has faulted its peers on shared hosts)."""
     import subprocess
     import sys

@@ -485,14 +485,20 @@ __global__ void __launch_bounds__(256) xrank_allreduce_kernel(const XrankAllredu
         const long long n4 = ap.count / 4;
         for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + t; i < n4;
              i += static_cast<long long>(gridDim.x) * blockDim.x) {
+            // all ranks' loads go out before the first one is used: one NVLink round trip, not `world`
+            float4 v[8];
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {
+                v[r] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (r < ap.world)
+                    asm volatile("ld.relaxed.sys.global.v4.f32 {%0,%1,%2,%3}, [%4];"
+                                 : "=f"(v[r].x), "=f"(v[r].y), "=f"(v[r].z), "=f"(v[r].w)
+                                 : "l"(reinterpret_cast<const float4 *>(ap.peer_src[r]) + i));
+            }
             float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-            for (int r = 0; r < ap.world; ++r) {
-                float4 v;
-                asm volatile("ld.relaxed.sys.global.v4.f32 {%0,%1,%2,%3}, [%4];"
-                             : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
-                             : "l"(reinterpret_cast<const float4 *>(ap.peer_src[r]) + i)
-                             : "memory");
-                acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+#pragma unroll
+            for (int r = 0; r < 8; ++r) {  // rank order: every rank computes the same bits
+                acc.x += v[r].x; acc.y += v[r].y; acc.z += v[r].z; acc.w += v[r].w;
             }
             float4 *d = reinterpret_cast<float4 *>(ap.dst) + i;
             float4 o = *d;

@@ -46,6 +46,7 @@ def parse():
     ap.add_argument("--batch", type=int, default=1)
     ap.add_argument("--layers", type=int, default=80)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-shapes", action="store_true", help="skip the per-shape table and the batch-32 line (N = 1 only)")
     return ap.parse_args()
 
 
@@ -123,6 +124,11 @@ def cpu_reference_sample(batch, reps=1):
 
     from oracle import dmm_oracle as o
 
+    # torchrun exports OMP_NUM_THREADS=1 to every rank: take all host cores explicitly
+    try:
+        torch.set_num_threads(os.cpu_count() or 1)
+    except RuntimeError:
+        pass
     cb16 = o.synthetic_codebook(42)
     table = (o.decode_table(o.cb16_to_cb64(cb16)).astype(np.float32) / 4)  # [65536, 8]
     table_t = torch.from_numpy(table)
@@ -181,6 +187,94 @@ def run_reference(args):
     }
     print(json.dumps(line), flush=True)
 
+
+# ------------------------------------------------------------------------------------------
+# single-shape timing (BASELINE.json configs[1..3] and the batch-32 half of the metric)
+# ------------------------------------------------------------------------------------------
+def time_shape(dmm, torch, family, batch, n, k, total_mb=700):
+    """Median microseconds per call over 5 replays of a CUDA graph of back-to-back calls (programmatic
+    dependent launch, atomic accumulation for the fp16 family), each call on another copy of the
+    weights so that together the copies exceed the L2 cache several times."""
+    code_bytes = n * k // 4
+    nbuf = max(2, min(64, int(total_mb * 1e6 // code_bytes) + 1))
+    gen = torch.Generator(device="cuda").manual_seed(1)
+    bufs = [torch.randint(-32768, 32768, (n, k // 8), dtype=torch.int16, device="cuda", generator=gen)
+            for _ in range(nbuf)]
+    if family == "fp16":
+        cb = dmm.synthetic_codebook(42, "cuda")
+        x = torch.randn(batch, k, device="cuda", dtype=torch.float16)
+        out = torch.zeros(batch, n, device="cuda", dtype=torch.float32)
+
+        def call(w):
+            dmm.decode_matmul_fp16(x, w, cb, 2.0 ** -10, out, accumulate=True, atomic=True, pdl=True)
+    else:
+        cb = dmm.build_codebook_abs("cuda")
+        x = torch.randint(-128, 128, (batch, k), dtype=torch.int8, device="cuda")
+        out = torch.zeros(batch, n, device="cuda", dtype=torch.int32)
+
+        def call(w):
+            dmm.decode_matmul_i8(x, w, cb, out, accumulate=True, pdl=True)
+    reps = max(nbuf * 2, 40)
+    call(bufs[0])
+    torch.cuda.synchronize()
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        call(bufs[0])
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            for i in range(reps):
+                call(bufs[i % nbuf])
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+        times = []
+        for _ in range(5):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            graph.replay()
+            e1.record(stream)
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1) * 1e3 / reps)
+    us = statistics.median(times)
+    del graph, bufs
+    return {"family": family, "batch": batch, "n": n, "k": k, "us": round(us, 2),
+            "gbs": round(code_bytes / us / 1e3, 1), "tflops": round(2 * batch * n * k / us / 1e6, 1),
+            "weight_copies": nbuf, "launches": reps}
+
+
+def per_shape_table(dmm, torch, peaks):
+    """BASELINE.json configs[1] (Llama-2-7B shapes, batch 1), configs[2] (batch sweep on the 7B gate/up
+    and down shapes), configs[3] (Llama-2-70B shapes at batch 1 and 16) and the integer operator."""
+    rows = []
+    for n, k in [(4096, 4096), (11008, 4096), (4096, 11008)]:
+        rows.append(dict(time_shape(dmm, torch, "fp16", 1, n, k), config="configs[1]"))
+    for n, k in [(11008, 4096), (4096, 11008)]:
+        for b in (2, 4, 8, 16, 32, 64):
+            rows.append(dict(time_shape(dmm, torch, "fp16", b, n, k), config="configs[2]"))
+    for n, k in [(10240, 8192), (8192, 8192), (28672, 8192), (8192, 28672)]:
+        for b in (1, 16):
+            rows.append(dict(time_shape(dmm, torch, "fp16", b, n, k), config="configs[3]"))
+    for b in (8, 32):
+        rows.append(dict(time_shape(dmm, torch, "int8", b, 28672, 8192), config="reference operator (int8)"))
+    hbm = float(peaks.get("hbm_gbs", 6650.0))
+    for r in rows:
+        r["frac_of_hbm_measured"] = round(r["gbs"] / hbm, 3)
+    return rows
+
+
+def batch_tensor_line(dmm, torch, peaks, batch, sampler_index):
+    """The batch-32 half of the metric: TFLOP/s of one 28672 x 8192 product at this batch, timed alone
+    (burst peak is the denominator), with its own clock record."""
+    sampler = ClockSampler(sampler_index)
+    sampler.start()
+    r = time_shape(dmm, torch, "fp16", batch, 28672, 8192, total_mb=1400)
+    clocks = sampler.stop()
+    burst = float(peaks.get("bf16_tflops", 1590.0))
+    return {"shape": [28672, 8192], "batch": batch, "us": r["us"], "tflops": r["tflops"],
+            "frac_of_bf16_burst": round(r["tflops"] / burst, 4), "peak_bf16_burst": burst,
+            "frac_of_2250": round(r["tflops"] / 2250.0, 4), "gbs": r["gbs"],
+            "kernel": "umma_kernel<PolF8,%d>" % (32 if batch <= 8 else 64 if batch <= 16 else 128),
+            "launches": r["launches"], "clocks": clocks}
 
 # ------------------------------------------------------------------------------------------
 # our arm
@@ -303,6 +397,38 @@ def run_ours(args):
     ms_kernels = timed(kgraph.replay, max(3, args.steps // 4))
     status = dmm.status()
 
+    # ---- parity of the fused step (what was timed) with the plain step, on a 2-block prefix ----
+    saved_layers = stack.layers
+    stack.layers = saved_layers[:2]
+    with torch.cuda.stream(stream):
+        h_a, h_b = h_in.clone(), h_in.clone()
+        stack.step(h_a, fused=True)
+        stack.step(h_b, fused=False)
+        stream.synchronize()
+    stack.layers = saved_layers
+    parity = {"what": "fused step (timed) vs plain step (separate cast / activation / residual kernels), first 2 blocks",
+              "max_abs_diff": float((h_a - h_b).abs().max()), "max_abs": float(h_b.abs().max())}
+    if world > 1:
+        t = torch.tensor([parity["max_abs_diff"]], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        parity["max_abs_diff"] = float(t.item())
+
+    peaks = {}
+    try:
+        peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+    except (OSError, ValueError):
+        pass
+    extra = {}
+    if world == 1 and not args.no_shapes:
+        del graph, graph_e2e, kgraph
+        with torch.cuda.stream(stream):
+            extra["batch32"] = batch_tensor_line(dmm, torch, peaks, 32, local)
+            extra["batch16"] = batch_tensor_line(dmm, torch, peaks, 16, local)
+            extra["per_shape"] = per_shape_table(dmm, torch, peaks)
+        extra["per_shape_how"] = ("CUDA events around a CUDA graph of back-to-back calls cycling over weight copies that "
+                                  "together exceed L2 several times; programmatic dependent launch; median of 5 replays")
+        status |= dmm.status()
+
     if rank == 0:
         from oracle import dmm_oracle  # noqa: F401  (the checker; used below for the CPU baseline only)
 
@@ -315,11 +441,6 @@ def run_ours(args):
             for lin in blk.values():
                 alg += lin.code_bytes + 2 * B * lin.in_features + 4 * B * lin.out_features + 4096
         n_launch = sum(len(blk) for blk in stack.layers)
-        peaks = {}
-        try:
-            peaks = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
-        except (OSError, ValueError):
-            pass
         peak = float(peaks.get("hbm_gbs", 6650.0))
         achieved = alg / (ms_kernels * 1e-3) / 1e9
         cpu = cpu_reference_sample(B, reps=1)
@@ -352,7 +473,9 @@ def run_ours(args):
             "cpu_baseline": cpu,
             "clocks": clocks,
             "status_word": status,
+            "parity": parity,
         }
+        line.update(extra)
         print(json.dumps(line), flush=True)
     if world > 1:
         # Captured graphs hold NCCL work; tearing the process group down under them can block.

@@ -1,4 +1,4 @@
-"""Codebook helpers: the E8P table, synthetic tables, int64 <-> fp16 views."""
+"""Codebook and input helpers: the E8P table, synthetic tables, int64 <-> fp16 views, random operands."""
 from __future__ import annotations
 
 from itertools import product
@@ -49,3 +49,14 @@ def synthetic_codebook(seed: int = 42, device="cpu") -> torch.Tensor:
     gen = torch.Generator().manual_seed(seed)
     m = torch.randint(0, 4, (256, 8), generator=gen)
     return (m.to(torch.float32) + 0.5).to(torch.float16).to(device)
+
+
+def build_x_weights(M: int, N: int, K: int, device):
+    """Random operands for the integer operator, as the reference's ``build_x_weights``
+    (test_decode_matmul.py:89-98): ``x`` int8 [M, K] uniform over the whole int8 range and LOGICAL
+    codes int16 [N, K/8] uniform over the whole int16 range, both drawn on ``device`` from
+    torch's global generator (seed it with ``torch.random.manual_seed``).  Tile-pack the codes
+    with ``transpose_tile`` before passing them to ``decode_matmul``."""
+    x = torch.randint(-128, 128, size=(M, K), dtype=torch.int8, device=device)
+    weights_compressed = torch.randint(-32768, 32768, size=(N, K // 8), dtype=torch.int16, device=device)
+    return x, weights_compressed

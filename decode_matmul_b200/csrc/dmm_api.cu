@@ -27,6 +27,7 @@ struct DeviceState {
 static std::mutex g_mutex;
 static DeviceState g_dev[kMaxDevices];
 static std::atomic<uint64_t> g_launches{0};
+static std::atomic<long long> g_xrank_wait_cycles{kWaitLimitCycles};  // dmm_set_wait_limit_ms
 
 static int current_device_state(DeviceState **out) {
     int dev = 0;
@@ -42,6 +43,10 @@ static int current_device_state(DeviceState **out) {
     *out = &d;
     return 0;
 }
+
+// Size of the library's own workspace on first use: tickets for N up to 2^24 (4 MiB), stream-K partials
+// at batch 64 (up to 256 CTAs: 16 MiB) and the activation planes for K up to 2^17 (16 MiB).
+constexpr size_t kDefaultWorkspace = size_t(40) << 20;
 
 static size_t ticket_bytes(long long N) {
     const size_t b = static_cast<size_t>(N / 16) * sizeof(unsigned);
@@ -78,20 +83,24 @@ static int resolve_workspace(DeviceState *d, long long M, long long N, long long
     }
     std::lock_guard<std::mutex> lock(g_mutex);
     if (d->workspace_bytes < need) {
-        // Work already enqueued may still use the old buffer: drain before replacing it.
-        cudaError_t err = cudaDeviceSynchronize();
+        // Allocation is not possible while the stream is being captured into a graph.
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        cudaError_t err = cudaStreamIsCapturing(stream, &cap);
         if (err != cudaSuccess) return err;
-        if (d->workspace) cudaFree(d->workspace);
-        d->workspace = nullptr;
-        d->workspace_bytes = 0;
-        const size_t bytes = need < (size_t(8) << 20) ? (size_t(8) << 20) : need;
-        err = cudaMalloc(&d->workspace, bytes);
+        if (cap != cudaStreamCaptureStatusNone) return DMM_ERR_WORKSPACE;
+        // The first allocation covers every call up to batch 64 and K = 131072 (kDefaultWorkspace).
+        // A later, larger need gets a new buffer; the old one is parked, never freed: kernels already
+        // enqueued and CUDA graphs captured earlier keep using it.
+        const size_t bytes = need < kDefaultWorkspace ? kDefaultWorkspace : need;
+        void *fresh = nullptr;
+        err = cudaMalloc(&fresh, bytes);
         if (err != cudaSuccess) return err;
-        err = cudaMemset(d->workspace, 0, bytes);
+        err = cudaMemsetAsync(fresh, 0, bytes, stream);  // the ticket counters start at zero
+        if (err == cudaSuccess) err = cudaStreamSynchronize(stream);
         if (err != cudaSuccess) return err;
+        d->workspace = fresh;  // (an outgrown buffer stays allocated until the process exits)
         d->workspace_bytes = bytes;
     }
-    (void)stream;
     *ws = d->workspace;
     return 0;
 }
@@ -433,6 +442,7 @@ int dmm_xrank_barrier(unsigned *const *peer_flags, int rank, int world, void *st
     bp.counter = d->xrank_counter;
     bp.rank = rank;
     bp.world = world;
+    bp.wait_limit = g_xrank_wait_cycles.load(std::memory_order_relaxed);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(1);
     cfg.blockDim = dim3(32);
@@ -478,6 +488,7 @@ int dmm_xrank_allreduce_add(float *dst, const float *const *peer_src, float *zer
     ap.count = count;
     ap.rank = rank;
     ap.world = world;
+    ap.wait_limit = g_xrank_wait_cycles.load(std::memory_order_relaxed);
     long long blocks = (count / 4 + 255) / 256;
     if (blocks > 16) blocks = 16;
     cudaLaunchConfig_t cfg = {};
@@ -551,6 +562,8 @@ int dmm_f16_noalloc(const void *x, const int16_t *codes, const void *cb16, float
     int rc = check_common(x, codes, cb16, out, M, N, K, sign_convention, DMM_LAYOUT_TILE);
     if (rc) return rc;
     if (M > kNoAllocMaxM || N > kNoAllocMaxN) return DMM_ERR_LIMIT;
+    // the scratch holds stream-K partials only: the atomic epilogue has no use for it and is not offered here
+    if (flags & ~(DMM_FLAG_ACCUMULATE | DMM_FLAG_PDL)) return DMM_ERR_ARG;
     DeviceState *d = nullptr;
     rc = current_device_state(&d);
     if (rc) return rc;
@@ -644,6 +657,12 @@ int dmm_select_path(int64_t M, int64_t N, int64_t K) {
     (void)N;
     (void)K;
     return DMM_PATH_TCGEN05_F8;
+}
+
+int dmm_set_wait_limit_ms(unsigned ms) {
+    // about 2 clock cycles per nanosecond; 0 restores the default (about a quarter of a second)
+    g_xrank_wait_cycles.store(ms == 0 ? kWaitLimitCycles : static_cast<long long>(ms) * 2000000ll, std::memory_order_relaxed);
+    return 0;
 }
 
 uint64_t dmm_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }

@@ -244,19 +244,26 @@ __host__ __device__ inline int epoch_tiles(uint32_t epoch_bytes, uint32_t tile_b
 constexpr uint32_t kUBarBytes = 2048;
 constexpr uint32_t kUTmemCols = 512;
 
+#ifndef DMM_EXP_NA
+#define DMM_EXP_NA 2
+#endif
+#ifndef DMM_EXP_NACC32
+#define DMM_EXP_NACC32 4
+#endif
 template <class Pol, int NMMA>
 struct UmmaPlan {
     // accumulators per MMA tile = active issuers: one per decoder group while the TMEM holds them
-    static constexpr int kNAcc = !Pol::kIsF8 ? 2 : (NMMA <= 32 ? 4 : (NMMA <= 64 ? 2 : 1));
+    static constexpr int kNAcc = !Pol::kIsF8 ? 2 : (NMMA <= 32 ? DMM_EXP_NACC32 : (NMMA <= 64 ? 2 : 1));
+    static constexpr int kNA = (Pol::kIsF8 && NMMA <= 32) ? DMM_EXP_NA : Pol::kNA;
     // issuer warps per accumulator: with fewer than four accumulators the two MMA tiles of a
     // group are issued by different warps (each accumulator still has exactly one issuer, so the
     // summation order stays fixed)
     static constexpr int kTileParts = kNAcc <= 2 ? 2 : 1;
     static constexpr uint32_t kDCols = 2 * kNAcc * NMMA;          // TMEM: accumulators first
     static constexpr uint32_t kBufCols = 2 * Pol::kG * Pol::kACols;  // one group buffer: [tile][k-tile][cols]
-    static constexpr uint32_t kACols = 4 * Pol::kNA * kBufCols;
+    static constexpr uint32_t kACols = 4 * kNA * kBufCols;
     static_assert(kDCols + kACols <= kUTmemCols, "TMEM plan exceeds 512 columns");
-    static constexpr int kSlots = 4 * Pol::kNA;                   // group buffers (= fp16 activation stages)
+    static constexpr int kSlots = 4 * kNA;                   // group buffers (= fp16 activation stages)
     static constexpr uint32_t kXStage = Pol::kG * Pol::x_tile_bytes(NMMA);
     // fp8 policy: the activation planes of a whole run of k-tiles ("epoch") stay resident in one
     // of kEpochs buffers, densely packed [tile][k-half][plane][row < M][16 B]
@@ -403,6 +410,7 @@ struct XrankBarrierParams {
     unsigned *flags[8];  // flags[t]: rank t's array of `world` words (peer pointers; [rank] is local)
     unsigned *counter;   // this rank's barrier counter (local)
     int rank, world;
+    long long wait_limit;  // clock cycles after which the wait gives up (DMM_STATUS_WAIT_TIMEOUT)
 };
 __global__ void __launch_bounds__(32) xrank_barrier_kernel(const XrankBarrierParams bp) {
     // Launched with programmatic stream serialization: the kernel after it may start at once (its
@@ -424,7 +432,7 @@ __global__ void __launch_bounds__(32) xrank_barrier_kernel(const XrankBarrierPar
             unsigned v;
             asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
             if (static_cast<int>(v - e) >= 0) break;
-            if (clock64() - t0 > kWaitLimitCycles) {
+            if (clock64() - t0 > bp.wait_limit) {
                 raise_status(DMM_STATUS_WAIT_TIMEOUT);
                 break;
             }
@@ -452,6 +460,7 @@ struct XrankAllreduceParams {
     float *zero_local;   // local, may be null
     long long count;     // floats, multiple of 4
     int rank, world;
+    long long wait_limit;  // clock cycles after which the wait gives up (DMM_STATUS_WAIT_TIMEOUT)
 };
 __global__ void __launch_bounds__(256) xrank_allreduce_kernel(const XrankAllreduceParams ap) {
     grid_dep_launch();
@@ -472,7 +481,7 @@ __global__ void __launch_bounds__(256) xrank_allreduce_kernel(const XrankAllredu
             unsigned v;
             asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
             if (static_cast<int>(v - e) >= 0) break;
-            if (clock64() - t0 > kWaitLimitCycles) {
+            if (clock64() - t0 > ap.wait_limit) {
                 raise_status(DMM_STATUS_WAIT_TIMEOUT);
                 failed = 1;
                 break;
@@ -551,7 +560,7 @@ __global__ void __launch_bounds__(128) planes_kernel(const void *x, int x_mode, 
 template <class Pol, int NMMA, bool kChain, bool kTp = false>
 __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const __grid_constant__ UmmaChainT<kChain ? kMaxOps : 1> ch) {
     using Plan = UmmaPlan<Pol, NMMA>;
-    constexpr int C = Pol::kC, G = Pol::kG, NA = Pol::kNA, RING = Pol::kRing, NACC = Plan::kNAcc, NB = Plan::kNB;
+    constexpr int C = Pol::kC, G = Pol::kG, NA = Plan::kNA, RING = Pol::kRing, NACC = Plan::kNAcc, NB = Plan::kNB;
     constexpr int TP = Plan::kTileParts;
 
     extern __shared__ __align__(1024) uint8_t smem_raw[];

@@ -11,7 +11,7 @@ from __future__ import annotations
 import torch
 
 from . import _lib, ops
-from .layout import shard_cols, shard_rows, transpose_tile
+from .layout import shard_cols, shard_fused_rows, transpose_tile
 
 
 class DecodeLinear:
@@ -62,11 +62,15 @@ class LinearStack:
         a = qkv(fp16(h));  h += o(fp16(a[:, :hidden]))          (attention itself is not part of
         g = gate_up(fp16(h));  h += down(fp16(silu(g0) * g1))    the operator: q stands in for it)
     Row-parallel outputs are summed over the tensor-parallel group before the residual add.
-    The weights are generated directly in sharded form: rank r of w draws its own codes, so
-    that no rank ever materialises a full matrix."""
+    By default the weights are generated directly in sharded form: rank r of w draws its own codes,
+    so that no rank ever materialises a full matrix (what the benchmark needs at 17 GB).  With
+    ``logical_seed`` every rank instead draws the same LOGICAL matrices from one seed and keeps its
+    shard of them (q, k, v and gate, up sharded part by part, o and down by reduction index, each
+    shard tile-packed on its own): the result then does not depend on the number of ranks, which is
+    what the tensor-parallel tests compare.  Meant for small configurations."""
 
     def __init__(self, cfg: dict, codebook_fp16: torch.Tensor, device, world: int = 1, rank: int = 0,
-                 seed: int = 46, scale: float = 2.0 ** -7, group=None):
+                 seed: int = 46, scale: float = 2.0 ** -7, group=None, logical_seed: int | None = None):
         self.cfg, self.world, self.rank, self.group = cfg, world, rank, group
         self.device = torch.device(device)
         self.hidden, self.ffn = cfg["hidden"], cfg["ffn"]
@@ -75,9 +79,14 @@ class LinearStack:
             div = n if name in ("qkv", "gate_up") else k
             if div % (32 * world) or (name in ("qkv", "gate_up") and n % (16 * world)):
                 raise RuntimeError(f"{name} does not shard over {world} ranks")
+        if (cfg["kv_heads"] * cfg["head_dim"]) % (16 * world) or cfg["hidden"] % (32 * world) or cfg["ffn"] % (32 * world):
+            raise RuntimeError(f"q/k/v or gate/up do not shard part by part over {world} ranks")
         self.shapes = shapes
         cb = codebook_fp16.to(self.device)
-        gen = torch.Generator(device=self.device).manual_seed(seed * 1000 + rank)
+        gen = torch.Generator(device=self.device).manual_seed(
+            logical_seed if logical_seed is not None else seed * 1000 + rank)
+        kv = cfg["kv_heads"] * cfg["head_dim"]
+        fused_parts = {"qkv": (cfg["hidden"], kv, kv), "gate_up": (cfg["ffn"], cfg["ffn"])}
         self.layers = []
         self.code_bytes_local = 0
         for _ in range(cfg["layers"]):
@@ -87,11 +96,20 @@ class LinearStack:
                     n_loc, k_loc = n // world, k
                 else:
                     n_loc, k_loc = n, k // world
-                # uniform int16 codes; any bit pattern is a valid tile-packed matrix, so the
-                # shard is drawn directly in tiled form
-                codes = torch.randint(-32768, 32768, (n_loc, k_loc // 8), dtype=torch.int16, device=self.device,
-                                      generator=gen)
-                block[name] = DecodeLinear(codes, cb, scale, tiled=True)
+                if logical_seed is not None:
+                    logical = torch.randint(-32768, 32768, (n, k // 8), dtype=torch.int16, device=self.device,
+                                            generator=gen)
+                    if name in fused_parts:
+                        mine = shard_fused_rows(logical, fused_parts[name], world, rank)
+                    else:
+                        mine = shard_cols(logical, world, rank)
+                    block[name] = DecodeLinear(mine.contiguous(), cb, scale)
+                else:
+                    # uniform int16 codes; any bit pattern is a valid tile-packed matrix, so the
+                    # shard is drawn directly in tiled form
+                    codes = torch.randint(-32768, 32768, (n_loc, k_loc // 8), dtype=torch.int16, device=self.device,
+                                          generator=gen)
+                    block[name] = DecodeLinear(codes, cb, scale, tiled=True)
                 self.code_bytes_local += block[name].code_bytes
             self.layers.append(block)
         self.code_bytes_total = sum(n * k // 4 for n, k in shapes.values()) * cfg["layers"]

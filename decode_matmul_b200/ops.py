@@ -269,5 +269,10 @@ def status(device=None) -> int:
     return v.value
 
 
+def set_wait_limit_ms(ms: int) -> None:
+    """Limit of the cross-rank waits (``dmm_set_wait_limit_ms``); 0 restores the default."""
+    _lib.check(_lib.lib().dmm_set_wait_limit_ms(int(ms)), "dmm_set_wait_limit_ms")
+
+
 def launch_count() -> int:
     return int(_lib.lib().dmm_launch_count())

@@ -242,6 +242,17 @@ int dmm_f16_noalloc(const void *x, const int16_t *codes, const void *cb16, float
 int dmm_decode(const int16_t *codes, const void *cb, int cb_is_f16, void *W_out, int64_t N,
                int64_t K, int sign_convention, int layout, void *stream);
 
+/*
+ * How long the cross-rank waits of dmm_xrank_barrier / dmm_xrank_allreduce_add may last before they
+ * give up, raise DMM_STATUS_WAIT_TIMEOUT and return (the kernel completes, the context stays usable):
+ * `ms` milliseconds at about 2 GHz, 0 = the default of about a quarter of a second.  Applies to calls
+ * enqueued afterwards, on every device.  A host that detects a lost rank on its own (heartbeat, store)
+ * can keep the limit short so that the surviving ranks' streams drain quickly.  This replaces the
+ * reference's only failure handling, gpuAssert -> exit() (decode_matmul_cuda.cu:35-42), for the
+ * multi-GPU step, which the reference does not have.
+ */
+int dmm_set_wait_limit_ms(unsigned ms);
+
 /* Bytes of workspace a call of dmm_i8 / dmm_f16 with these sizes needs (0 if none). */
 size_t dmm_workspace_bytes(int64_t M, int64_t N, int64_t K);
 

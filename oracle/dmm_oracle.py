@@ -205,3 +205,20 @@ def fast_unpack(packed: np.ndarray) -> np.ndarray:
     a = packed.reshape(n // 32, k8 // 2, 32, 2)
     a = a.transpose(0, 2, 1, 3)
     return np.ascontiguousarray(a).reshape(n, k8)
+
+
+def convert_sign_convention(codes: np.ndarray, src: int, dst: int) -> np.ndarray:
+    """codes such that decode(result, dst) == decode(codes, src), for every code word.
+
+    Both conventions encode an even-parity vector of eight signs in seven stored bits
+    (``decode_matmul_cuda.cu:50-53``: the parity is the sign of weight 7;
+    ``fast_decode_matmul_cuda.cu:52-53``: of weight 0), so the map is a bijection."""
+    c = np.asarray(codes).view(np.uint16).astype(np.uint32)
+    if src == dst:
+        return np.asarray(codes).copy()
+    s7 = (c >> 8) & 0x7F
+    par = np.zeros_like(s7)
+    for b in range(7):
+        par ^= (s7 >> b) & 1
+    new = (s7 >> 1) | (par << 6) if src == SIGN_SLOW else ((s7 << 1) & 0x7F) | par
+    return ((c & 0x80FF) | (new << 8)).astype(np.uint16).view(np.int16)

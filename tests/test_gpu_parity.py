@@ -428,54 +428,88 @@ def test_linear_stack_chained_step_matches_plain():
 _TP_WORKER = r"""
 import os, sys
 sys.path.insert(0, sys.argv[1])
+import numpy as np
 import torch, torch.distributed as dist
 import decode_matmul_b200 as dmm
 from decode_matmul_b200.linear import LinearStack
+from oracle import dmm_oracle as o
 rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
 torch.cuda.set_device(rank)
+dev = f"cuda:{rank}"
 dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
 cfg = dict(hidden=1024, kv_heads=2, head_dim=64, ffn=2048, layers=3)
 cb = dmm.synthetic_codebook(42)
+sc = 2.0 ** -8
 ok = True
+
+def oracle_block(stack1, h):
+    # one block of the UNSHARDED model on the CPU (float64), the data flow of LinearStack.step
+    blk, cbn = stack1.layers[0], cb.numpy()
+    lin = lambda name, x16: o.decode_matmul_f16(np.ascontiguousarray(x16), o.tile_unpack(blk[name].codes.cpu().numpy()), cbn, sc).astype(np.float64)
+    a = lin("qkv", h.astype(np.float16))
+    h = h + lin("o", a[:, :cfg["hidden"]].astype(np.float16))
+    g = lin("gate_up", h.astype(np.float16))
+    f = cfg["ffn"]
+    return h + lin("down", (g[:, :f] / (1 + np.exp(-g[:, :f])) * g[:, f:]).astype(np.float16))
+
 for B in (1, 5):
-    stack = LinearStack(cfg, cb, f"cuda:{rank}", world=world, rank=rank, seed=9, scale=2.0 ** -8)
     torch.manual_seed(1)
-    h0 = torch.randn(B, cfg["hidden"], device=f"cuda:{rank}")
+    h0 = torch.randn(B, cfg["hidden"], device=dev)
     dist.broadcast(h0, 0)
+    # the same LOGICAL weights on every rank count: the unsharded model on this GPU is the reference
+    whole = LinearStack(cfg, cb, dev, world=1, rank=0, logical_seed=9, scale=sc)
+    want = whole.step(h0.clone(), fused=True)
+    stack = LinearStack(cfg, cb, dev, world=world, rank=rank, logical_seed=9, scale=sc)
     peer = stack._peer_state(B)
-    outs = [stack.step(h0.clone(), fused=True) for _ in range(3)]          # one-shot all-reduce kernel (default)
+    outs = {"pull": [stack.step(h0.clone(), fused=True) for _ in range(3)]}   # one-shot all-reduce kernel
     os.environ["DMM_TP_MODE"] = "push"
-    push = LinearStack(cfg, cb, f"cuda:{rank}", world=world, rank=rank, seed=9, scale=2.0 ** -8)
-    outs += [push.step(h0.clone(), fused=True) for _ in range(3)]          # adds into every rank's buffer from the epilogue
+    push = LinearStack(cfg, cb, dev, world=world, rank=rank, logical_seed=9, scale=sc)
+    outs["push"] = [push.step(h0.clone(), fused=True) for _ in range(3)]      # epilogues add into every rank's buffer
     os.environ["DMM_TP_MODE"] = "pull"
     os.environ["DMM_TP_PEER"] = "0"
-    ref = LinearStack(cfg, cb, f"cuda:{rank}", world=world, rank=rank, seed=9, scale=2.0 ** -8).step(h0.clone(), fused=True)
+    nccl = LinearStack(cfg, cb, dev, world=world, rank=rank, logical_seed=9, scale=sc)
+    outs["nccl"] = [nccl.step(h0.clone(), fused=True)]
     os.environ["DMM_TP_PEER"] = "1"
     torch.cuda.synchronize()
-    err = max(float((o - ref).abs().max()) for o in outs)
-    ok = ok and peer is not None and err <= 2e-3 * max(1.0, float(ref.abs().max())) and dmm.status() == 0
-    print(f"rank {rank} B={B} peer={peer is not None} err={err:.3e}", flush=True)
+    tol = 2e-3 * max(1.0, float(want.abs().max()))
+    for mode, hs in outs.items():
+        err = max(float((h - want).abs().max()) for h in hs)
+        ok = ok and err <= tol
+        print(f"rank {rank} B={B} world={world} {mode} vs world=1: max abs diff {err:.3e} (tol {tol:.1e})", flush=True)
+    # one block against the CPU oracle, sharded over the ranks (pull form) and unsharded
+    cfg1 = dict(cfg, layers=1)
+    one = LinearStack(cfg1, cb, dev, world=1, rank=0, logical_seed=9, scale=sc)
+    one_tp = LinearStack(cfg1, cb, dev, world=world, rank=rank, logical_seed=9, scale=sc)
+    ref = oracle_block(one, h0.cpu().numpy().astype(np.float64))
+    e1 = float(np.abs(one.step(h0.clone(), fused=True).cpu().numpy() - ref).max())
+    e2 = float(np.abs(one_tp.step(h0.clone(), fused=True).cpu().numpy() - ref).max())
+    ok = ok and peer is not None and e1 <= 2e-3 and e2 <= 2e-3 and dmm.status() == 0
+    print(f"rank {rank} B={B} one block vs oracle: world=1 {e1:.3e}, world={world} {e2:.3e}, peer memory {peer is not None}", flush=True)
+    del stack, push, nccl, one_tp
 dist.barrier(); torch.cuda.synchronize()
 print("TP_OK" if ok else "TP_FAIL", flush=True)
+sys.stdout.flush()
 os._exit(0 if ok else 1)
 """
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_tensor_parallel_peer_memory_step_matches_nccl(tmp_path):
-    """Two ranks (one process per GPU): the fused step summed over the ranks by the one-shot
-    all-reduce kernel (partials pulled over peer memory) and by epilogues that add into every rank's
-    residual buffer, both against the same step summed with NCCL all-reduce.  NVLS is off (a rank that died while its memory was bound to an NVLink group object
-    has faulted its peers on shared hosts)."""
+def test_tensor_parallel_step_matches_one_gpu_and_oracle(tmp_path):
+    """Two ranks (one process per GPU) share ONE set of logical weights (LinearStack logical_seed): the
+    fused step summed over the ranks by the one-shot all-reduce kernel (pull), by epilogues that add
+    into every rank's residual buffer (push) and by NCCL all-reduce must each equal the step of the
+    unsharded model on one GPU, and one block must equal the CPU oracle.  NVLS is off (a rank that
+    died while its memory was bound to an NVLink group object has faulted its peers on shared hosts)."""
     import subprocess
     import sys
 
     script = tmp_path / "tp_worker.py"
     script.write_text(_TP_WORKER)
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
     res = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
                           "--master-addr", "127.0.0.1", "--master-port", "29533", str(script), root],
                          capture_output=True, text=True, timeout=600, env=env)
-    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
+    print(res.stdout[-3000:])
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-2000:]
     assert res.stdout.count("TP_OK") == 2

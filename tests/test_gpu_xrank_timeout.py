@@ -1,0 +1,60 @@
+"""The bounded cross-rank waits, made to run out on ONE GPU without faulting anything: a world of two
+whose second rank does not exist (its flag words are ordinary local memory that nobody writes).
+The kernel must give up after the configured limit, raise DMM_STATUS_WAIT_TIMEOUT, finish normally,
+and leave the context usable for the next call.  Needs a B200."""
+import time
+
+import pytest
+import torch
+
+import decode_matmul_b200 as dmm
+from decode_matmul_b200 import _lib
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture()
+def short_limit():
+    dmm.set_wait_limit_ms(5)
+    yield
+    dmm.set_wait_limit_ms(0)
+
+
+def test_rank_barrier_gives_up_when_a_rank_never_arrives(short_limit):
+    dev = torch.device("cuda")
+    mine = torch.zeros(64, dtype=torch.int32, device=dev)
+    ghost = torch.zeros(64, dtype=torch.int32, device=dev)  # the flag words of a rank that never runs
+    assert dmm.status() == 0
+    t0 = time.perf_counter()
+    dmm.xrank_barrier([mine.data_ptr(), ghost.data_ptr()], 0, dev)
+    st = dmm.status()  # synchronises
+    assert time.perf_counter() - t0 < 1.0, "the wait did not end within its limit"
+    assert st & _lib.STATUS_WAIT_TIMEOUT
+    assert int(ghost[0]) != 0, "this rank did signal the other one before waiting"
+    # the context is intact: a barrier of a world of one completes, and so does a product
+    dmm.xrank_barrier([mine.data_ptr()], 0, dev)
+    assert dmm.status() == 0
+    x = torch.randn(1, 256, device=dev, dtype=torch.float16)
+    w = torch.randint(-32768, 32768, (64, 32), dtype=torch.int16, device=dev)
+    y = dmm.decode_matmul_fp16(x, w, dmm.synthetic_codebook(42, dev), 1.0)
+    assert torch.isfinite(y).all() and dmm.status() == 0
+
+
+def test_allreduce_kernel_gives_up_and_leaves_the_destination_alone(short_limit):
+    dev = torch.device("cuda")
+    mine = torch.zeros(64, dtype=torch.int32, device=dev)
+    ghost = torch.zeros(64, dtype=torch.int32, device=dev)
+    src0 = torch.full((1, 8192), 2.0, device=dev)
+    src1 = torch.full((1, 8192), 3.0, device=dev)
+    dst = torch.full((1, 8192), 1.0, device=dev)
+    t0 = time.perf_counter()
+    dmm.xrank_allreduce_add(dst, [src0.data_ptr(), src1.data_ptr()], [mine.data_ptr(), ghost.data_ptr()], 0)
+    st = dmm.status()
+    assert time.perf_counter() - t0 < 1.0
+    assert st & _lib.STATUS_WAIT_TIMEOUT
+    assert torch.equal(dst, torch.full_like(dst, 1.0)), "nothing may be summed when a rank is missing"
+    # a world of one afterwards: dst += src0, and the partial buffer named by `zero` is cleared
+    flags1 = torch.zeros(64, dtype=torch.int32, device=dev)
+    dmm.xrank_allreduce_add(dst, [src0.data_ptr()], [flags1.data_ptr()], 0, zero=src1)
+    assert dmm.status() == 0
+    assert torch.equal(dst, torch.full_like(dst, 3.0)) and float(src1.abs().sum()) == 0.0

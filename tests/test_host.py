@@ -116,3 +116,40 @@ def test_fast_layout_packers_match_oracle():
     assert torch.equal(layout.fast_unpack(packed), t)
     with pytest.raises(RuntimeError):
         layout.fast_pack(t[:48])  # N % 32
+
+
+def test_sign_convention_converter_is_lossless_on_every_code_word(golden):
+    """decode(convert(c, src, dst), dst) == decode(c, src) for all 65 536 code words, both ways:
+    the slow map (decode_matmul_cuda.cu:50-53) and the fast map (fast_decode_matmul_cuda.cu:52-53)
+    both encode an even-parity sign vector, so the conversion is a bijection."""
+    codes = np.arange(65536, dtype=np.uint16).view(np.int16)
+    cb = np.ascontiguousarray(golden["e8p_codebook"]["codebook_abs"])
+    slow, fast = o.decode_table(cb, o.SIGN_SLOW), o.decode_table(cb, o.SIGN_FAST)
+    assert np.array_equal(slow, golden["decode_all_codes"]["table"])  # the pinned side
+    t = torch.from_numpy(codes)
+    to_fast = dmm.convert_sign_convention(t, dmm.SIGN_SLOW, dmm.SIGN_FAST).numpy()
+    to_slow = dmm.convert_sign_convention(t, dmm.SIGN_FAST, dmm.SIGN_SLOW).numpy()
+    assert np.array_equal(fast[to_fast.view(np.uint16)], slow)
+    assert np.array_equal(slow[to_slow.view(np.uint16)], fast)
+    assert np.array_equal(to_fast, o.convert_sign_convention(codes, o.SIGN_SLOW, o.SIGN_FAST))
+    assert np.array_equal(to_slow, o.convert_sign_convention(codes, o.SIGN_FAST, o.SIGN_SLOW))
+    back = dmm.convert_sign_convention(torch.from_numpy(to_fast), dmm.SIGN_FAST, dmm.SIGN_SLOW)
+    assert torch.equal(back, t)
+    assert len(np.unique(to_fast.view(np.uint16))) == 65536
+    # index byte and shift bit are untouched
+    assert np.array_equal(to_fast.view(np.uint16) & 0x80FF, codes.view(np.uint16) & 0x80FF)
+    with pytest.raises(RuntimeError):
+        dmm.convert_sign_convention(t.to(torch.int32), 0, 1)
+
+
+def test_build_x_weights_shapes_and_ranges():
+    """Same contract as the reference's input builder (test_decode_matmul.py:89-98)."""
+    torch.random.manual_seed(42)
+    x, w = dmm.build_x_weights(8, 64, 4096, "cpu")
+    assert x.dtype == torch.int8 and tuple(x.shape) == (8, 4096)
+    assert w.dtype == torch.int16 and tuple(w.shape) == (64, 512)
+    assert int(x.min()) == -128 and int(x.max()) == 127
+    assert int(w.min()) < -32000 and int(w.max()) > 32000
+    torch.random.manual_seed(42)
+    x2, w2 = dmm.build_x_weights(8, 64, 4096, "cpu")
+    assert torch.equal(x, x2) and torch.equal(w, w2)

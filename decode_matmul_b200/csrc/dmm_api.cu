@@ -9,6 +9,7 @@
 #include "dmm_launch.h"
 #include "dmm_stream.cuh"
 #include "dmm_umma.cuh"
+#include "dmm_tc.cuh"
 
 namespace dmm {
 
@@ -247,7 +248,9 @@ static int run_umma(bool f8, const void *x, int x_kind, long long x_ld, long lon
 #ifdef DMM_TRACE
         p.trace = g_trace;
 #endif
-        rc = launch_umma(f8, p, d->num_sms, pdl, stream);
+        // 17 to 32 batch rows (128 MMA columns) run on the kernel of dmm_tc.cuh, measured faster there;
+        // everything else on the kernel of dmm_umma.cuh
+        rc = (f8 && p.M > 16) ? launch_tc_wide(p, d->num_sms, pdl, stream) : launch_umma(f8, p, d->num_sms, pdl, stream);
         g_launches.fetch_add(1, std::memory_order_relaxed);
         if (rc) return rc;
     }

@@ -276,12 +276,12 @@ __host__ __device__ inline uint64_t sign_mask(uint32_t h, int convention, int fm
 
 // kFmtFp6 masks carry two bits per weight, so they are stored as ONE 32-bit word per high
 // byte: weights 0..3 at bits 8j+1 (sign ^ shift) and 8j+5 (sign), weights 4..7 one bit
-// higher.  (word & 0x22222222) and ((word >> 1) & 0x22222222) are the two byte-mask words.
+// lower.  (word & 0x22222222) and ((word << 1) & 0x22222222) are the two byte-mask words.
 // A 4-byte look-up is one shared-memory wavefront per warp instead of two.
 __host__ __device__ inline uint32_t sign_mask_fp6_packed(uint32_t h, int convention) {
     const uint64_t m = sign_mask(h, convention, kFmtFp6);
     const uint32_t lo = static_cast<uint32_t>(m), hi = static_cast<uint32_t>(m >> 32);
-    return (lo & 0x22222222u) | ((hi & 0x22222222u) << 1);
+    return (lo & 0x22222222u) | ((hi & 0x22222222u) >> 1);
 }
 
 // Codebook entry e as packed int8 x 8 (= 4 * value), from either table format.  Sets *bad
@@ -364,12 +364,14 @@ __device__ inline bool lut_fill(uint32_t lut_addr, const void *cb, int cb_is_f16
 struct LutLane {
     uint32_t entry_c;  // lut_addr | (lane%16)*8
     uint32_t mask_c;   // lut_addr | 128 | (lane%16)*8, or | lane*4 for packed masks
+    uint32_t two;      // the number 2 in a register the compiler cannot see through (keeps a multiply a multiply)
 };
 
 __device__ __forceinline__ LutLane lut_lane(uint32_t lut_addr, int lane, bool packed_mask = false) {
     LutLane l;
     l.entry_c = lut_addr | (static_cast<uint32_t>(lane & 15) << 3);
     l.mask_c = packed_mask ? (lut_addr | 128u | (static_cast<uint32_t>(lane) << 2)) : (l.entry_c | 128u);
+    l.two = 2u;
     return l;
 }
 
@@ -380,7 +382,9 @@ __device__ __forceinline__ uint2 decode8_fp6(uint32_t word, const LutLane &l) {
     constexpr uint32_t sel_hi = which == 0 ? 0x7614u : 0x7634u;
     const uint2 e = lds64(prmt(word, l.entry_c, sel_idx));
     const uint32_t m = lds32(prmt(word, l.mask_c, sel_hi));
-    return make_uint2(e.x ^ (m & 0x22222222u), e.y ^ ((m >> 1) & 0x22222222u));
+    uint32_t m2;  // m << 1 as an integer multiply-add: the FMA pipe is idle, the integer ALU is not
+    asm("mad.lo.u32 %0, %1, %2, 0;" : "=r"(m2) : "r"(m), "r"(l.two));
+    return make_uint2(e.x ^ (m & 0x22222222u), e.y ^ (m2 & 0x22222222u));
 }
 
 // Decodes the code in half `which` (0 = low 16 bits, 1 = high) of `word`: 8 packed bytes.

@@ -214,8 +214,8 @@ struct PolF16 {
     static constexpr int out_cols(int nmma) { return nmma; }
 };
 
-constexpr int kUDecWarps = 16, kUMmaWarp = 16, kUMmaWarps = 4, kULoadWarps = 4, kULoadTeams = 2, kUTmaWarp = 24;
-constexpr int kUThreads = (kUDecWarps + kUMmaWarps + kULoadWarps + 1) * 32;
+constexpr int kUDecWarps = 16, kUMmaWarp = 16, kUMmaWarps = 4, kULoadWarps = 4, kULoadTeams = 2, kUTmaWarp = 24, kUTmaWarps = 4;
+constexpr int kUThreads = (kUDecWarps + kUMmaWarps + kULoadWarps + kUTmaWarps) * 32;
 constexpr int kFirstEpoch = 16;  // k-tiles in the first activation epoch of a CTA at batch 1 (fp8 policy)
 constexpr int kMaxEpoch = 48;    // and at most this many in the later ones: short epochs keep the
                                  // loaders' latency per epoch below the time the previous one lasts
@@ -244,17 +244,11 @@ __host__ __device__ inline int epoch_tiles(uint32_t epoch_bytes, uint32_t tile_b
 constexpr uint32_t kUBarBytes = 2048;
 constexpr uint32_t kUTmemCols = 512;
 
-#ifndef DMM_EXP_NA
-#define DMM_EXP_NA 2
-#endif
-#ifndef DMM_EXP_NACC32
-#define DMM_EXP_NACC32 4
-#endif
 template <class Pol, int NMMA>
 struct UmmaPlan {
     // accumulators per MMA tile = active issuers: one per decoder group while the TMEM holds them
-    static constexpr int kNAcc = !Pol::kIsF8 ? 2 : (NMMA <= 32 ? DMM_EXP_NACC32 : (NMMA <= 64 ? 2 : 1));
-    static constexpr int kNA = (Pol::kIsF8 && NMMA <= 32) ? DMM_EXP_NA : Pol::kNA;
+    static constexpr int kNAcc = !Pol::kIsF8 ? 2 : (NMMA <= 32 ? 4 : (NMMA <= 64 ? 2 : 1));
+    static constexpr int kNA = Pol::kNA;
     // issuer warps per accumulator: with fewer than four accumulators the two MMA tiles of a
     // group are issued by different warps (each accumulator still has exactly one issuer, so the
     // summation order stays fixed)
@@ -557,8 +551,10 @@ __global__ void __launch_bounds__(128) planes_kernel(const void *x, int x_mode, 
 // kChain == false is the plain single-product kernel: the op loops below run once with every
 // per-op value a compile-time-known kernel parameter.
 // kTp == true adds the tensor-parallel pieces (adds into every rank's buffer, residual move).
-template <class Pol, int NMMA, bool kChain, bool kTp = false>
-__global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const __grid_constant__ UmmaChainT<kChain ? kMaxOps : 1> ch) {
+// kSplit == true is the instantiation with four TMA producer warps (28 warps; the register budget per
+// thread is smaller, which only the 32-column fp16-family kernel tolerates without a slow-down).
+template <class Pol, int NMMA, bool kChain, bool kTp = false, bool kSplit = false>
+__global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps - 1) * 32, 1) umma_kernel(const __grid_constant__ UmmaChainT<kChain ? kMaxOps : 1> ch) {
     using Plan = UmmaPlan<Pol, NMMA>;
     constexpr int C = Pol::kC, G = Pol::kG, NA = Plan::kNA, RING = Pol::kRing, NACC = Plan::kNAcc, NB = Plan::kNB;
     constexpr int TP = Plan::kTileParts;
@@ -614,7 +610,8 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const __grid_constan
     // barriers, allocate TMEM and zero the fp16 activation stages meanwhile and then go on
     // (the code stream starts flowing while the table is still being built).  The decoders
     // join through barrier 4, on which the others only arrive.
-    constexpr int kOtherThreads = kUThreads - kUDecWarps * 32;
+    // 25 warps (one TMA producer) or 28 (four, one per decoder group: batch 1 and 2 of the fp16 family)
+    constexpr int n_threads = kSplit ? kUThreads : kUThreads - (kUTmaWarps - 1) * 32, n_other = n_threads - kUDecWarps * 32;
     bool bad_cb = false;
     if (warp < kUDecWarps) {
         if (tid == 0) DMM_STAMP(0, 1, 0);
@@ -622,9 +619,9 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const __grid_constan
                           Pol::kIsF8 != 0 && !Pol::kIsInt, Pol::kIsInt ? nullptr : &cb_pre);
         if (tid == 0) DMM_STAMP(0, 1, 1);
         if (lane == 0) DMM_STAMP(0, 8 + warp, 0);
-        named_barrier(4, kUThreads);
+        named_barrier(4, n_threads);
     } else {
-        const int ot = tid - kUDecWarps * 32;  // 0 .. kOtherThreads-1
+        const int ot = tid - kUDecWarps * 32;  // 0 .. n_other-1
         const int bt = ot - kUMmaWarps * 32;   // loader and TMA warps initialise the barriers
         if (bt == 0) DMM_STAMP(0, 3, 0);
         if (bt >= 0 && bt < Plan::kBarCount) {
@@ -641,20 +638,21 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const __grid_constan
             if (bt == 0) {
                 flags[0] = 0;
                 flags[1] = 0;
+                flags[2] = 2;
             }
             fence_mbar_init();
         }
         if (warp == kUMmaWarp) tmem_alloc(smem_u32(const_cast<uint32_t *>(tmem_slot)), kUTmemCols);
         if constexpr (!Pol::kIsF8) {  // fp16 stages: rows past the batch must read as zero
-            for (uint32_t o = ot * 16u; o < Plan::kXBytes; o += kOtherThreads * 16u) sts128(x_addr + o, make_uint4(0, 0, 0, 0));
+            for (uint32_t o = ot * 16u; o < Plan::kXBytes; o += n_other * 16u) sts128(x_addr + o, make_uint4(0, 0, 0, 0));
         }
         fence_async_smem();
         tc_fence_before();
         if (ot == 0) DMM_STAMP(0, 2, 2);
         if (bt == 0) DMM_STAMP(0, 3, 1);
-        named_barrier(3, kOtherThreads);
+        named_barrier(3, n_other);
         if (bt == 0) DMM_STAMP(0, 3, 2);
-        named_barrier_arrive(4, kUThreads);
+        named_barrier_arrive(4, n_threads);
         if (bt == 0) DMM_STAMP(0, 2, 1);
     }
     tc_fence_after();
@@ -670,7 +668,8 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const __grid_constan
         const int q = warp >> 2, wq = warp & 3;
         const uint32_t gring = ring_addr + static_cast<uint32_t>(q) * (RING * Plan::kSlotBytes);  // ring of group q
         if (bad_cb) raise_status(DMM_STATUS_BAD_CODEBOOK);
-        const LutLane ll = lut_lane(lut_addr, lane, Pol::kIsF8 != 0 && !Pol::kIsInt);
+        LutLane ll = lut_lane(lut_addr, lane, Pol::kIsF8 != 0 && !Pol::kIsInt);
+        ll.two = static_cast<uint32_t>(flags[2]);
         if (tid == 0) DMM_STAMP(0, 0, 2);
 
         const uint32_t tlane = tmem + (static_cast<uint32_t>(wq * 32) << 16);
@@ -1042,11 +1041,52 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const __grid_constan
             }
             }  // op
         }
-    } else if (warp == kUTmaWarp) {
-        // =============================== TMA producer ===============================
-        // One thread streams the codes: chunk after chunk in the CTA-wide chunk order, each chunk
-        // one tiled load (16 strips x C k-tiles) into the ring of the decoder group it belongs to.
-        // Always the full box: k-tiles past the segment are not used, strips past N read as zero.
+    } else if (warp >= kUTmaWarp) {
+        // =============================== TMA producers ===============================
+        // They stream the codes: chunk after chunk in the CTA-wide chunk order, each chunk one tiled load
+        // (16 strips x C k-tiles) into the ring of the decoder group it belongs to.  Always the full box:
+        // k-tiles past the segment are not used, strips past N read as zero.
+        // Up to two batch rows four threads share the work, one per decoder group (four short independent
+        // loops: a group whose ring is full does not hold up the others; measured 1 % faster at batch 1);
+        // from three rows on one thread serves all groups in order (measured faster there).
+        const int pw = warp - kUTmaWarp;
+        constexpr bool split = kSplit;
+        if (split) {
+            const int q = pw;
+            if (lane == 0) {
+                const uint64_t policy = policy_evict_first();
+                uint32_t n_q = 0;      // chunks issued for this group
+                int slot = 0;          // n_q % RING
+                uint32_t par = 1;      // parity of the Empty phase that frees `slot` (first pass: nothing to wait for)
+                int cbase = 0;
+                const UmmaParams &p = ch.op[0];
+                DMM_OP_GEOMETRY(p);
+                (void)p;
+                for (int ss = ss_first; ss <= ss_last; cbase += seg_chunks(ss), ++ss) {
+                    const int nchunks = seg_chunks(ss), kt0 = seg_kt0(ss);
+                    for (int c = (q - cbase) & 3; c < nchunks; c += 4) {
+                        if (n_q >= RING) mbar_wait(bar(Plan::kBarEmpty + q * RING + slot), par, flags);
+                        const uint32_t b = bar(Plan::kBarCode + q * RING + slot);
+                        mbar_arrive_expect_tx(b, Plan::kSlotBytes);
+                        tma_load_2d(ring_addr + (q * RING + slot) * Plan::kSlotBytes, &ch.map[0], (kt0 + c * C) * 32, ss * 16, b, policy);
+                        ++n_q;
+                        if (++slot == RING) {
+                            slot = 0;
+                            par ^= 1u;
+                        }
+                    }
+                }
+                if (flags[0]) {
+                    // A wait gave up somewhere: loads may still be in flight.  Give the last load of
+                    // every ring slot a bounded chance to land before the CTA releases its shared memory.
+                    for (uint32_t d = 0; d < RING && d < n_q; ++d) {
+                        const uint32_t idx = n_q - 1 - d;
+                        mbar_wait_limit(bar(Plan::kBarCode + q * RING + static_cast<int>(idx % RING)), (idx / RING) & 1,
+                                        20ll * 1000 * 1000);
+                    }
+                }
+            }
+        } else if (pw == 0) {
         if (lane == 0) {
             const uint64_t policy = policy_evict_first();
             uint32_t cnt[4] = {0, 0, 0, 0};  // chunks issued per decoder group
@@ -1080,6 +1120,7 @@ __global__ void __launch_bounds__(kUThreads, 1) umma_kernel(const __grid_constan
                                         20ll * 1000 * 1000);
                     }
             }
+        }
         }
     } else {
         // =========================== activation loaders ===========================
@@ -1334,8 +1375,17 @@ template <class Pol, int NMMA, bool kChain>
 inline int launch_umma_ops(const UmmaParams *ops, int n_ops, unsigned *sync, int num_sms, bool pdl, cudaStream_t stream) {
     using Plan = UmmaPlan<Pol, NMMA>;
     auto kernel = umma_kernel<Pol, NMMA, kChain, false>;
+    // four TMA producer warps up to two batch rows of the fp16 family (measured 1 % faster at batch 1), else one
+    bool split = false;
     if constexpr (Pol::kIsF8 && !kChain) {  // tensor-parallel epilogue: its own instantiation, nothing of it in the plain kernel
         if (ops[0].n_peers > 0 || ops[0].move_count > 0) kernel = umma_kernel<Pol, NMMA, kChain, true>;
+    }
+    if constexpr (Pol::kIsF8 && !Pol::kIsInt && !kChain && NMMA == 32) {
+        if (ops[0].M <= 2) {
+            split = true;
+            kernel = umma_kernel<Pol, NMMA, kChain, false, true>;
+            if (ops[0].n_peers > 0 || ops[0].move_count > 0) kernel = umma_kernel<Pol, NMMA, kChain, true, true>;
+        }
     }
     cudaError_t err =
         cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Plan::kDynBytes));
@@ -1362,7 +1412,7 @@ inline int launch_umma_ops(const UmmaParams *ops, int n_ops, unsigned *sync, int
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid);
-    cfg.blockDim = dim3(kUThreads);
+    cfg.blockDim = dim3(split ? kUThreads : kUThreads - (kUTmaWarps - 1) * 32);
     cfg.dynamicSmemBytes = Plan::kDynBytes;
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];

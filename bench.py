@@ -381,13 +381,14 @@ def run_ours(args):
             hk.zero_()
             stack.step(hk)
             return
-        for blk in stack.layers:
-            for k, lin in blk.items():
-                if B <= 32:
-                    dmm.decode_matmul_fp16(xs[k], lin.codes, lin.codebook, lin.scale, outs[k], accumulate=True,
-                                           atomic=True, pdl=True)
-                else:
-                    lin(xs[k], out=outs[k])
+        flat = [(k, lin) for blk in stack.layers for k, lin in blk.items()]
+        for i, (k, lin) in enumerate(flat):
+            if B <= 32:
+                dmm.hint_next_weights(flat[i + 1][1].codes if i + 1 < len(flat) else None)  # as the step does
+                dmm.decode_matmul_fp16(xs[k], lin.codes, lin.codebook, lin.scale, outs[k], accumulate=True,
+                                       atomic=True, pdl=True)
+            else:
+                lin(xs[k], out=outs[k])
 
     with torch.cuda.stream(stream):
         kernels_only()

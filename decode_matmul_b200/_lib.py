@@ -18,7 +18,7 @@ STATUS_WAIT_TIMEOUT, STATUS_BAD_CODEBOOK, STATUS_BAD_SMEM = 1, 2, 4
 
 EXPORTS = (
     "dmm_i8", "dmm_f16", "dmm_f16_fused", "dmm_f16_fused_tp", "dmm_xrank_barrier", "dmm_xrank_allreduce_add", "dmm_f16_chain", "dmm_f16_noalloc", "dmm_decode", "dmm_workspace_bytes", "dmm_status", "dmm_select_path",
-    "dmm_set_wait_limit_ms", "dmm_launch_count", "dmm_error_string", "dmm_version",
+    "dmm_hint_next_weights", "dmm_set_wait_limit_ms", "dmm_launch_count", "dmm_error_string", "dmm_version",
 )
 
 
@@ -72,6 +72,8 @@ def lib() -> ctypes.CDLL:
     L.dmm_status.restype = ci
     L.dmm_select_path.argtypes = [i64, i64, i64]
     L.dmm_select_path.restype = ci
+    L.dmm_hint_next_weights.argtypes = [vp, i64, i64]
+    L.dmm_hint_next_weights.restype = ci
     L.dmm_set_wait_limit_ms.argtypes = [cu]
     L.dmm_set_wait_limit_ms.restype = ci
     L.dmm_launch_count.argtypes = []

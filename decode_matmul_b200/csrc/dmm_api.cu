@@ -28,6 +28,13 @@ struct DeviceState {
 static std::mutex g_mutex;
 static DeviceState g_dev[kMaxDevices];
 static std::atomic<uint64_t> g_launches{0};
+// dmm_hint_next_weights: what the calling host thread said its next-but-one product will stream
+struct NextHint {
+    const void *codes = nullptr;
+    long long N = 0, K = 0;
+};
+static thread_local NextHint t_next_hint;
+
 static std::atomic<long long> g_xrank_wait_cycles{kWaitLimitCycles};  // dmm_set_wait_limit_ms
 
 static int current_device_state(DeviceState **out) {
@@ -244,6 +251,12 @@ static int run_umma(bool f8, const void *x, int x_kind, long long x_ld, long lon
         if (tp != nullptr) {
             p.n_peers = tp->n_peers;
             for (int r = 0; r < tp->n_peers; ++r) p.peer_out[r] = tp->peer_out[r] + static_cast<size_t>(m0) * N;
+        }
+        if (m0 + step >= M && t_next_hint.codes != nullptr) {  // the last launch of this call prefetches for the next call
+            p.next_codes = t_next_hint.codes;
+            p.next_N = t_next_hint.N;
+            p.next_K = t_next_hint.K;
+            t_next_hint = NextHint();
         }
 #ifdef DMM_TRACE
         p.trace = g_trace;
@@ -665,6 +678,14 @@ int dmm_select_path(int64_t M, int64_t N, int64_t K) {
 int dmm_set_wait_limit_ms(unsigned ms) {
     // about 2 clock cycles per nanosecond; 0 restores the default (about a quarter of a second)
     g_xrank_wait_cycles.store(ms == 0 ? kWaitLimitCycles : static_cast<long long>(ms) * 2000000ll, std::memory_order_relaxed);
+    return 0;
+}
+
+int dmm_hint_next_weights(const int16_t *codes, int64_t N, int64_t K) {
+    if (codes != nullptr && (N < 16 || K < 32 || N % 16 != 0 || K % 32 != 0 || !aligned16(codes))) return DMM_ERR_SHAPE;
+    t_next_hint.codes = codes;
+    t_next_hint.N = N;
+    t_next_hint.K = K;
     return 0;
 }
 

@@ -581,6 +581,7 @@ __global__ void __launch_bounds__(kTcThreads, 1) dmm_kernel(const __grid_constan
                     }
                 }
             }
+            prefetch_next_codes(p, cta, q, 4, 4 * RING * C);
             if (flags[0]) {
                 // A wait gave up somewhere: loads may still be in flight.  Give the last load of
                 // every ring slot a bounded chance to land before the CTA releases its shared memory.
@@ -750,6 +751,17 @@ inline int launch_tc(const UmmaParams &params, int num_sms, bool pdl, cudaStream
     if (T < num_sms) grid = static_cast<unsigned>(T);
     p.part.a = static_cast<int>(T / grid);
     p.part.b = static_cast<int>(T % grid);
+    if (p.next_codes != nullptr) {
+        const long long Tn = ((p.next_N / 16 + 15) / 16) * (p.next_K / 32);
+        const long long gn = Tn < num_sms ? Tn : num_sms;
+        if (Tn >= (1ll << 31) || gn <= 0) {
+            p.next_codes = nullptr;
+        } else {
+            p.next_grid = static_cast<int>(gn);
+            p.next_part.a = static_cast<int>(Tn / gn);
+            p.next_part.b = static_cast<int>(Tn % gn);
+        }
+    }
     const int rc = make_codes_map(&args.map, p.codes, p.N, p.K, Plan::kC);
     if (rc) return rc;
     cudaLaunchConfig_t cfg = {};

@@ -322,6 +322,14 @@ struct UmmaParams {
     long long zero_count;
     Part32 part;         // tiles per CTA: part.a = T / grid, part.b = T % grid
     unsigned dyn_smem_bytes;
+    // Optional hint: the code matrix of the NEXT product of the stream (dmm_hint_next_weights).  When this
+    // kernel's TMA producers have issued their last load they fetch, into L2 only, the first ring fill that
+    // CTA `blockIdx.x` of that next launch will ask for, so that its first codes -- the longest wait of a
+    // launch's prologue -- come from L2 instead of DRAM.
+    const void *next_codes;
+    long long next_N, next_K;
+    Part32 next_part;
+    int next_grid;
     long long *trace;    // debugging aid (builds with -DDMM_TRACE only): clock stamps of CTA 0
 };
 
@@ -1076,6 +1084,7 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
                         }
                     }
                 }
+                prefetch_next_codes(ch.op[0], cta, q, 4, 4 * RING * C);
                 if (flags[0]) {
                     // A wait gave up somewhere: loads may still be in flight.  Give the last load of
                     // every ring slot a bounded chance to land before the CTA releases its shared memory.
@@ -1110,6 +1119,7 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
                 }
             }
             }  // op
+            prefetch_next_codes(ch.op[n_ops - 1], cta, 0, 1, 4 * RING * C);
             if (flags[0]) {
                 // A wait gave up somewhere: loads may still be in flight.  Give the last load of
                 // every ring slot a bounded chance to land before the CTA releases its shared memory.
@@ -1335,6 +1345,27 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
     if (warp == kUMmaWarp) tmem_dealloc(tmem, kUTmemCols);
 }
 
+// L2 prefetch of the first `tiles` k-tiles (at most) that CTA `cta` of the next launch will stream: for each
+// of the 16 strips of its first super-tile one contiguous run of the strip's code stream.  `part` of the
+// strips (part of 4) is done by the caller, so that four producer threads can share the work.
+__device__ __forceinline__ void prefetch_next_codes(const UmmaParams &p, int cta, int part, int nparts, int tiles) {
+    if (p.next_codes == nullptr || cta >= p.next_grid) return;
+    const int KT = static_cast<int>(p.next_K / 32);
+    const int i0 = part32_begin(p.next_part, cta), i1 = part32_begin(p.next_part, cta + 1);
+    const int ss = i0 / KT, kt0 = i0 - ss * KT;
+    int n = i1 - i0 < tiles ? i1 - i0 : tiles;
+    if (n > KT - kt0) n = KT - kt0;  // (a range that wraps into the next super-tile: its first part only)
+    if (n <= 0) return;
+    const long long strips = p.next_N / 16;
+    const uint8_t *base = reinterpret_cast<const uint8_t *>(p.next_codes);
+    for (int s = part; s < 16; s += nparts) {
+        const long long strip = static_cast<long long>(ss) * 16 + s;
+        if (strip >= strips) break;
+        const uint8_t *src = base + (strip * KT + kt0) * 128;
+        asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(static_cast<uint32_t>(n) * 128u) : "memory");
+    }
+}
+
 // cuTensorMapEncodeTiled through the runtime's driver entry point (no link-time libcuda).
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
@@ -1407,6 +1438,17 @@ inline int launch_umma_ops(const UmmaParams *ops, int n_ops, unsigned *sync, int
         if (T >= (1ll << 31)) return DMM_ERR_SHAPE;
         p.part.a = static_cast<int>(T / grid);
         p.part.b = static_cast<int>(T % grid);
+        if (p.next_codes != nullptr) {
+            const long long Tn = ((p.next_N / 16 + 15) / 16) * (p.next_K / 32);
+            const long long gn = Tn < num_sms ? Tn : num_sms;
+            if (Tn >= (1ll << 31) || gn <= 0) {
+                p.next_codes = nullptr;
+            } else {
+                p.next_grid = static_cast<int>(gn);
+                p.next_part.a = static_cast<int>(Tn / gn);
+                p.next_part.b = static_cast<int>(Tn % gn);
+            }
+        }
         const int rc = make_codes_map(&ch.map[i], p.codes, p.N, p.K, Pol::kC);
         if (rc) return rc;
     }

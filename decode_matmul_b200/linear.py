@@ -238,13 +238,21 @@ class LinearStack:
         part, cur = peer["res"], peer["cur"]
         a.zero_()
         kw = dict(accumulate=True, atomic=True, pdl=True)
-        for blk in self.layers:
+        from . import ops as _ops
+
+        hint = lambda w: _ops.hint_next_weights(w)
+        for i, blk in enumerate(self.layers):
             q, o, gu, dn = blk["qkv"], blk["o"], blk["gate_up"], blk["down"]
+            nxt = self.layers[i + 1]["qkv"].codes if i + 1 < len(self.layers) else None
+            hint(o.codes)
             mm(h, q.codes, q.codebook, q.scale, a, x_kind=_lib.X_F32, zero=g, **kw)
+            hint(gu.codes)
             mm(a, o.codes, o.codebook, o.scale, part[cur], x_kind=_lib.X_F32, **kw)
             xrank_allreduce_add(h, peer["res_ptrs"][cur], peer["flag_ptrs"], self.rank, zero=part[1 - cur])
             cur = 1 - cur
+            hint(dn.codes)
             mm(h, gu.codes, gu.codebook, gu.scale, g, x_kind=_lib.X_F32, zero=a, **kw)
+            hint(nxt)
             mm(g, dn.codes, dn.codebook, dn.scale, part[cur], x_kind=_lib.X_F32_SILU_MUL, x_gap=ffn_loc, **kw)
             xrank_allreduce_add(h, peer["res_ptrs"][cur], peer["flag_ptrs"], self.rank, zero=part[1 - cur])
             cur = 1 - cur
@@ -292,17 +300,27 @@ class LinearStack:
                                  x_kind=_lib.X_F32_SILU_MUL, x_gap=ffn_loc)]
                 decode_matmul_chain(ops, self.layers[b0]["qkv"].codebook, pdl=True)
             return h
-        for blk in self.layers:
+        from . import ops as _ops
+
+        hint = lambda w: _ops.hint_next_weights(w)
+        for i, blk in enumerate(self.layers):
             q, o, gu, dn = blk["qkv"], blk["o"], blk["gate_up"], blk["down"]
+            nxt = self.layers[i + 1]["qkv"].codes if i + 1 < len(self.layers) else None
             kw = dict(accumulate=True, atomic=True, pdl=True)
+            # before every product: which weights the product after it will stream (its kernel prefetches
+            # their first codes into L2, so the next launch does not start with a DRAM round trip)
+            hint(o.codes)
             mm(h, q.codes, q.codebook, q.scale, a, x_kind=_lib.X_F32, zero=g, **kw)
+            hint(gu.codes)
             if tp:
                 mm(a, o.codes, o.codebook, o.scale, po, x_kind=_lib.X_F32, zero=pd, **kw)
                 torch.distributed.all_reduce(po, group=self.group)
                 h.add_(po)
             else:
                 mm(a, o.codes, o.codebook, o.scale, h, x_kind=_lib.X_F32, **kw)
+            hint(dn.codes)
             mm(h, gu.codes, gu.codebook, gu.scale, g, x_kind=_lib.X_F32, zero=a, **kw)
+            hint(nxt)
             if tp:
                 mm(g, dn.codes, dn.codebook, dn.scale, pd, x_kind=_lib.X_F32_SILU_MUL, x_gap=ffn_loc, zero=po, **kw)
                 torch.distributed.all_reduce(pd, group=self.group)

@@ -269,6 +269,17 @@ def status(device=None) -> int:
     return v.value
 
 
+def hint_next_weights(weights_compressed) -> None:
+    """Tells the library which weight matrix the product AFTER the next one will stream (``dmm_hint_next_weights``):
+    the next product's kernel then prefetches that matrix's first codes into L2.  ``None`` clears the hint."""
+    if weights_compressed is None:
+        _lib.check(_lib.lib().dmm_hint_next_weights(None, 0, 0), "dmm_hint_next_weights")
+        return
+    _check_input(weights_compressed, "weights_compressed", torch.int16)
+    n, k8 = weights_compressed.shape
+    _lib.check(_lib.lib().dmm_hint_next_weights(_ptr(weights_compressed), n, k8 * 8), "dmm_hint_next_weights")
+
+
 def set_wait_limit_ms(ms: int) -> None:
     """Limit of the cross-rank waits (``dmm_set_wait_limit_ms``); 0 restores the default."""
     _lib.check(_lib.lib().dmm_set_wait_limit_ms(int(ms)), "dmm_set_wait_limit_ms")

@@ -243,6 +243,18 @@ int dmm_decode(const int16_t *codes, const void *cb, int cb_is_f16, void *W_out,
                int64_t K, int sign_convention, int layout, void *stream);
 
 /*
+ * Hint for a sequence of products on one stream (the layers of a model): `codes` [N, K/8] (tile layout) is
+ * the weight matrix of the product AFTER the next one this host thread enqueues.  The next dmm_f16 /
+ * dmm_f16_fused / dmm_f16_fused_tp call of this thread consumes the hint: towards the end of its kernel
+ * every CTA fetches into L2 (no other effect) the first codes that the same CTA of the following launch
+ * will stream, so that the following launch does not begin with a DRAM round trip -- about a microsecond of
+ * every launch's prologue at batch 1.  Purely a performance hint: results do not depend on it, a stale or
+ * wrong hint only wastes a little bandwidth (the memory must be readable), NULL clears it.  The reference
+ * has no counterpart (one product per call, decode_matmul_cuda.cu:178-234).
+ */
+int dmm_hint_next_weights(const int16_t *codes, int64_t N, int64_t K);
+
+/*
  * How long the cross-rank waits of dmm_xrank_barrier / dmm_xrank_allreduce_add may last before they
  * give up, raise DMM_STATUS_WAIT_TIMEOUT and return (the kernel completes, the context stays usable):
  * `ms` milliseconds at about 2 GHz, 0 = the default of about a quarter of a second.  Applies to calls

@@ -17,7 +17,7 @@ X_F16, X_F32, X_F32_SILU_MUL = 0, 1, 2
 STATUS_WAIT_TIMEOUT, STATUS_BAD_CODEBOOK, STATUS_BAD_SMEM = 1, 2, 4
 
 EXPORTS = (
-    "dmm_i8", "dmm_f16", "dmm_f16_fused", "dmm_f16_fused_tp", "dmm_xrank_barrier", "dmm_xrank_allreduce_add", "dmm_f16_chain", "dmm_f16_noalloc", "dmm_decode", "dmm_workspace_bytes", "dmm_status", "dmm_select_path",
+    "dmm_i8", "dmm_f16", "dmm_f16_fused", "dmm_f16_fused_tp", "dmm_f16_tp_produce", "dmm_f16_tp_consume", "dmm_tp_finalize", "dmm_xrank_barrier", "dmm_xrank_allreduce_add", "dmm_f16_chain", "dmm_f16_noalloc", "dmm_decode", "dmm_workspace_bytes", "dmm_status", "dmm_select_path",
     "dmm_hint_next_weights", "dmm_set_wait_limit_ms", "dmm_launch_count", "dmm_error_string", "dmm_version",
 )
 
@@ -56,6 +56,12 @@ def lib() -> ctypes.CDLL:
     L.dmm_f16_fused_tp.argtypes = [vp, ci, i64, i64, vp, vp, ctypes.c_float, vp, ci, i64, i64, i64, ci, cu, vp, i64, vp, vp,
                                    i64, vp]
     L.dmm_f16_fused_tp.restype = ci
+    L.dmm_f16_tp_produce.argtypes = [vp, ci, i64, i64, vp, vp, ctypes.c_float, vp, vp, ci, ci, i64, i64, i64, ci, cu, vp]
+    L.dmm_f16_tp_produce.restype = ci
+    L.dmm_f16_tp_consume.argtypes = [vp, vp, i64, vp, vp, ci, i64, vp, vp, ctypes.c_float, vp, i64, i64, i64, ci, cu, vp, i64, vp]
+    L.dmm_f16_tp_consume.restype = ci
+    L.dmm_tp_finalize.argtypes = [vp, vp, vp, vp, ci, i64, vp]
+    L.dmm_tp_finalize.restype = ci
     L.dmm_xrank_barrier.argtypes = [vp, ci, ci, vp]
     L.dmm_xrank_barrier.restype = ci
     L.dmm_xrank_allreduce_add.argtypes = [vp, vp, vp, i64, vp, ci, ci, vp]

@@ -198,6 +198,11 @@ struct TpArgs {
     int n_peers = 0;
     float *move_src = nullptr, *move_dst = nullptr;
     long long move_count = 0;
+    // slots form (dmm_f16_tp_produce / dmm_f16_tp_consume)
+    int mode = 0, rank = 0, world = 0;
+    unsigned *const *flags = nullptr;
+    long long count = 0;
+    float *h_out = nullptr;
 };
 
 static int run_umma(bool f8, const void *x, int x_kind, long long x_ld, long long x_gap, const void *codes,
@@ -216,7 +221,7 @@ static int run_umma(bool f8, const void *x, int x_kind, long long x_ld, long lon
         UmmaParams p = {};
         p.x = reinterpret_cast<const uint8_t *>(x) + static_cast<size_t>(m0) * x_ld * (x_kind == DMM_X_F16 ? 2 : 4);
         p.M = M - m0 < step ? M - m0 : step;
-        if (f8 && p.M >= kPlanesMinBatch) {
+        if (f8 && p.M >= kPlanesMinBatch && !(tp != nullptr && tp->mode == 3)) {
             // split the activations into E5M2 planes once, instead of once per CTA inside the kernel
             uint8_t *planes = reinterpret_cast<uint8_t *>(ws) + planes_offset(M, N, d->num_sms);
             rc = launch_planes(p.x, x_kind, x_ld, x_gap, static_cast<int>(p.M), K, planes, pdl, stream);
@@ -248,9 +253,21 @@ static int run_umma(bool f8, const void *x, int x_kind, long long x_ld, long lon
                 p.move_count = tp->move_count;
             }
         }
-        if (tp != nullptr) {
+        if (tp != nullptr && tp->mode == 0) {
             p.n_peers = tp->n_peers;
             for (int r = 0; r < tp->n_peers; ++r) p.peer_out[r] = tp->peer_out[r] + static_cast<size_t>(m0) * N;
+        }
+        if (tp != nullptr && tp->mode != 0) {
+            p.tp_mode = tp->mode;
+            p.tp_rank = tp->rank;
+            p.tp_world = tp->world;
+            p.tp_count = tp->count;
+            p.tp_wait = g_xrank_wait_cycles.load(std::memory_order_relaxed);
+            p.h_out = tp->h_out;
+            for (int r = 0; r < tp->world; ++r) {
+                p.peer_out[r] = tp->peer_out[r];
+                p.tp_flags[r] = tp->flags[r];
+            }
         }
         if (m0 + step >= M && t_next_hint.codes != nullptr) {  // the last launch of this call prefetches for the next call
             p.next_codes = t_next_hint.codes;
@@ -433,6 +450,101 @@ int dmm_f16_fused_tp(const void *x, int x_kind, int64_t x_ld, int64_t x_gap, con
     return run_umma(true, x, x_kind, x_ld, x_gap, codes, cb16, scale, peer_out[0], M, N, K, sign_convention,
                     flags | DMM_FLAG_ATOMIC | DMM_FLAG_ACCUMULATE, nullptr, 0, static_cast<cudaStream_t>(stream), zero_ptr,
                     zero_count, &tp);
+}
+
+static int check_tp_group(float *const *peer_slots, unsigned *const *peer_flags, int rank, int world) {
+    if (!peer_slots || !peer_flags) return DMM_ERR_NULL;
+    if (world < 1 || world > 8 || rank < 0 || rank >= world) return DMM_ERR_ARG;
+    for (int r = 0; r < world; ++r) {
+        if (!peer_slots[r] || !peer_flags[r]) return DMM_ERR_NULL;
+        if (!aligned16(peer_slots[r]) || !aligned16(peer_flags[r])) return DMM_ERR_ALIGN;
+    }
+    return 0;
+}
+
+int dmm_f16_tp_produce(const void *x, int x_kind, int64_t x_ld, int64_t x_gap, const int16_t *codes, const void *cb16,
+                       float scale, float *const *peer_slots, unsigned *const *peer_flags, int rank, int world, int64_t M,
+                       int64_t N, int64_t K, int sign_convention, unsigned flags, void *stream) {
+    int rc = check_tp_group(peer_slots, peer_flags, rank, world);
+    if (rc) return rc;
+    rc = check_common(x, codes, cb16, peer_slots[rank], M, N, K, sign_convention, DMM_LAYOUT_TILE);
+    if (rc) return rc;
+    if (M > 8) return DMM_ERR_LIMIT;
+    if (x_kind != DMM_X_F16 && x_kind != DMM_X_F32 && x_kind != DMM_X_F32_SILU_MUL) return DMM_ERR_ARG;
+    if (x_ld < K || x_ld % 8 != 0 || x_gap % 4 != 0 || (x_kind == DMM_X_F32_SILU_MUL && x_gap + K > x_ld))
+        return DMM_ERR_SHAPE;
+    if (flags & ~DMM_FLAG_PDL) return DMM_ERR_ARG;
+    TpArgs tp;
+    tp.mode = 2;
+    tp.rank = rank;
+    tp.world = world;
+    tp.peer_out = peer_slots;
+    tp.flags = peer_flags;
+    tp.count = M * N;
+    return run_umma(true, x, x_kind, x_ld, x_gap, codes, cb16, scale, peer_slots[rank], M, N, K, sign_convention,
+                    flags | DMM_FLAG_ATOMIC | DMM_FLAG_ACCUMULATE, nullptr, 0, static_cast<cudaStream_t>(stream), nullptr, 0, &tp);
+}
+
+int dmm_f16_tp_consume(const float *h_in, float *h_out, int64_t x_ld, const float *slots, const unsigned *flags_local,
+                       int world, int64_t slot_count, const int16_t *codes, const void *cb16, float scale, float *out,
+                       int64_t M, int64_t N, int64_t K, int sign_convention, unsigned flags, float *zero_ptr,
+                       int64_t zero_count, void *stream) {
+    if (!h_in || !h_out || !slots || !flags_local) return DMM_ERR_NULL;
+    if (world < 1 || world > 8) return DMM_ERR_ARG;
+    int rc = check_common(h_in, codes, cb16, out, M, N, K, sign_convention, DMM_LAYOUT_TILE);
+    if (rc) return rc;
+    if (M > 8) return DMM_ERR_LIMIT;
+    if (!aligned16(h_out) || !aligned16(slots) || !aligned16(flags_local)) return DMM_ERR_ALIGN;
+    if (x_ld != K || slot_count != M * K) return DMM_ERR_SHAPE;  // the residual stream is [M, K], a slot one copy of it
+    if (zero_count < 0 || (zero_count > 0 && zero_ptr == nullptr)) return DMM_ERR_ARG;
+    // the kernel finds "this rank's" slot array and flag words in entry `rank` of the per-rank tables:
+    // a consumer only ever touches its own, so every entry names them and the rank is 0
+    float *slot_tab[8];
+    unsigned *flag_tab[8];
+    for (int r = 0; r < 8; ++r) {
+        slot_tab[r] = const_cast<float *>(slots);
+        flag_tab[r] = const_cast<unsigned *>(flags_local);
+    }
+    TpArgs tp;
+    tp.mode = 3;
+    tp.rank = 0;
+    tp.world = world;
+    tp.peer_out = slot_tab;
+    tp.flags = flag_tab;
+    tp.count = slot_count;
+    tp.h_out = h_out;
+    return run_umma(true, h_in, DMM_X_F32, x_ld, 0, codes, cb16, scale, out, M, N, K, sign_convention,
+                    flags | DMM_FLAG_ATOMIC | DMM_FLAG_ACCUMULATE, nullptr, 0, static_cast<cudaStream_t>(stream), zero_ptr,
+                    zero_count, &tp);
+}
+
+int dmm_tp_finalize(const float *h_in, float *h_out, const float *slots, const unsigned *flags_local, int world,
+                    int64_t count, void *stream) {
+    if (!h_in || !h_out || !slots || !flags_local) return DMM_ERR_NULL;
+    if (world < 1 || world > 8) return DMM_ERR_ARG;
+    if (count < 4 || count % 4 != 0) return DMM_ERR_SHAPE;
+    if (!aligned16(h_in) || !aligned16(h_out) || !aligned16(slots)) return DMM_ERR_ALIGN;
+    TpFinalizeParams fp = {};
+    fp.h_in = h_in;
+    fp.h_out = h_out;
+    fp.slots = slots;
+    fp.flags = flags_local;
+    fp.count = count;
+    fp.world = world;
+    fp.wait_limit = g_xrank_wait_cycles.load(std::memory_order_relaxed);
+    long long blocks = (count / 4 + 255) / 256;
+    if (blocks > 16) blocks = 16;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(blocks));
+    cfg.blockDim = dim3(256);
+    cfg.stream = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return cudaLaunchKernelEx(&cfg, tp_finalize_kernel, fp);
 }
 
 int dmm_xrank_barrier(unsigned *const *peer_flags, int rank, int world, void *stream) {

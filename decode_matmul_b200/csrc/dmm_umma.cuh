@@ -315,6 +315,14 @@ struct UmmaParams {
     // so that the sum over ranks needs no separate all-reduce; see dmm_f16_fused_tp.
     float *peer_out[8];
     int n_peers;
+    // Tensor-parallel "slots" form (tp_mode 2 = producer, 3 = consumer; see dmm_f16_tp_produce / _consume):
+    // peer_out[r] is then the base of rank r's slot array [2 parities][world][tp_count] and tp_flags[r] its
+    // flag words; words 16 and 17 of this rank's own flag array are its epoch counter and arrival ticket.
+    int tp_mode, tp_rank, tp_world;
+    unsigned *tp_flags[8];
+    long long tp_count;    // floats per slot = M * N of the row-parallel products
+    long long tp_wait;     // clock cycles after which the consumer's flag wait gives up
+    float *h_out;          // consumer: where the summed residual stream is written ([M, x_ld])
     float *move_src;     // optional: move_dst[i] += move_src[i], then move_src[i] = 0 (this rank's copy of the
     float *move_dst;     // residual stream changing buffers), done by the loaders like the clearing below
     long long move_count;
@@ -362,6 +370,39 @@ struct UmmaChainT {
 #else
 #define DMM_STAMP(role, idx, what) do { } while (0)
 #endif
+
+// Residual stream plus the partial products that every rank of a tensor-parallel group has pushed into
+// this rank's slots (consumer side of the slots form): eight consecutive values of one row, summed in
+// rank order; the sum is also written to h_out, and returned rounded to fp16.
+__device__ __forceinline__ void load_piece_sum(const float *h_in, float *h_out, const float *slots, int world,
+                                               long long slot_stride, long long x_ld, int row, long long k0, uint32_t (&h)[4]) {
+    const long long off = row * x_ld + k0;
+    float4 a0 = __ldcg(reinterpret_cast<const float4 *>(h_in + off));
+    float4 a1 = __ldcg(reinterpret_cast<const float4 *>(h_in + off + 4));
+    float4 v0[8], v1[8];
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {
+        v0[r] = make_float4(0.f, 0.f, 0.f, 0.f);
+        v1[r] = v0[r];
+        if (r < world) {
+            v0[r] = __ldcg(reinterpret_cast<const float4 *>(slots + r * slot_stride + off));
+            v1[r] = __ldcg(reinterpret_cast<const float4 *>(slots + r * slot_stride + off + 4));
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < 8; ++r) {  // rank order: every rank computes the same bits
+        a0.x += v0[r].x; a0.y += v0[r].y; a0.z += v0[r].z; a0.w += v0[r].w;
+        a1.x += v1[r].x; a1.y += v1[r].y; a1.z += v1[r].z; a1.w += v1[r].w;
+    }
+    *reinterpret_cast<float4 *>(h_out + off) = a0;
+    *reinterpret_cast<float4 *>(h_out + off + 4) = a1;
+    const float f[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const __half2 hh = __floats2half2_rn(f[2 * j], f[2 * j + 1]);
+        h[j] = *reinterpret_cast<const uint32_t *>(&hh);
+    }
+}
 
 // Eight consecutive activations of one row as four packed half2 words, from any input kind.
 __device__ __forceinline__ void load_piece(const void *xp, int x_mode, long long x_ld, long long x_gap, int row,
@@ -531,6 +572,54 @@ __global__ void __launch_bounds__(256) xrank_allreduce_kernel(const XrankAllredu
     }
 }
 
+// End of a tensor-parallel step in the slots form: h_out = h_in + the partial products of the last epoch
+// from every rank's slot (what a consumer's loaders do on the fly, as a kernel of its own).
+struct TpFinalizeParams {
+    const float *h_in;
+    float *h_out;
+    const float *slots;      // this rank's slot array [2][world][count]
+    const unsigned *flags;   // this rank's flag words; word 16 = epoch counter
+    long long count;
+    int world;
+    long long wait_limit;
+};
+__global__ void __launch_bounds__(256) tp_finalize_kernel(const TpFinalizeParams fp) {
+    grid_dep_launch();
+    grid_dep_wait();
+    const int t = threadIdx.x;
+    const unsigned e = *reinterpret_cast<volatile const unsigned *>(fp.flags + 16);
+    if (t < fp.world) {
+        const long long t0 = clock64();
+        for (;;) {
+            unsigned v;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(fp.flags + t) : "memory");
+            if (static_cast<int>(v - e) >= 0) break;
+            if (clock64() - t0 > fp.wait_limit) {
+                raise_status(DMM_STATUS_WAIT_TIMEOUT);
+                break;
+            }
+            __nanosleep(40);
+        }
+    }
+    __syncthreads();
+    const float *sl = fp.slots + static_cast<long long>(e & 1u) * fp.world * fp.count;
+    const long long n4 = fp.count / 4;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + t; i < n4; i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        float4 a = __ldcg(reinterpret_cast<const float4 *>(fp.h_in) + i);
+        float4 v[8];
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+            v[r] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (r < fp.world) v[r] = __ldcg(reinterpret_cast<const float4 *>(sl + r * fp.count) + i);
+        }
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+            a.x += v[r].x; a.y += v[r].y; a.z += v[r].z; a.w += v[r].w;
+        }
+        reinterpret_cast<float4 *>(fp.h_out)[i] = a;
+    }
+}
+
 // Splits the activations of one call into E5M2 planes ONCE, in the layout the tcgen05 kernel's
 // epoch buffers use: [k-tile][k-half][plane][row < rows_padded][16 B].  With more than a few
 // batch rows the per-CTA split inside umma_kernel (every CTA repeats it for its k range) costs
@@ -681,6 +770,14 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
         if (tid == 0) DMM_STAMP(0, 0, 2);
 
         const uint32_t tlane = tmem + (static_cast<uint32_t>(wq * 32) << 16);
+        // Tensor-parallel producer: this launch is epoch e = counter + 1 (every CTA reads the counter before
+        // the last CTA to finish moves it on) and accumulates into this rank's own slot of parity e & 1.
+        [[maybe_unused]] unsigned tp_epoch = 0;
+        [[maybe_unused]] float *tp_slot_mine = nullptr;
+        if (kTp && p0.tp_mode == 2) {
+            tp_epoch = *reinterpret_cast<volatile const unsigned *>(p0.tp_flags[p0.tp_rank] + 16) + 1u;
+            tp_slot_mine = p0.peer_out[p0.tp_rank] + (static_cast<long long>(tp_epoch & 1u) * p0.tp_world + p0.tp_rank) * p0.tp_count;
+        }
         // The four groups share the shared-memory look-up pipe and are otherwise independent:
         // start them a fraction of a group apart so that one group's hand-over and waiting
         // falls into the others' look-up bursts instead of all groups idling together.
@@ -783,7 +880,8 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
                 Acc v[NB];
 #pragma unroll
                 for (int b = 0; b < NB; ++b) v[b] = Acc(0);
-                Acc *const out_acc = reinterpret_cast<Acc *>(p.out);
+                Acc *out_acc = reinterpret_cast<Acc *>(p.out);
+                if (kTp && p.tp_mode == 2) out_acc = reinterpret_cast<Acc *>(tp_slot_mine);
                 Acc *const partials_acc = reinterpret_cast<Acc *>(p.partials);
                 if (Pol::kIsF8 && !Pol::kIsInt && p.M == 1) {
                     // batch 1: only column 8 * plane of every accumulator carries data; fetch those
@@ -903,6 +1001,42 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
                 }
                 if (tid == 0) DMM_STAMP(4, segidx, 2);
             }
+        }
+        if (kTp && p.tp_mode == 2 && q < 2) {
+            // Tensor-parallel producer, after this CTA's last atomic adds: the last CTA of the grid to get
+            // here copies this rank's finished partial product into its slot on every other rank (plain
+            // vector stores over NVLink: one value per element and peer) and then raises this rank's flag
+            // on every rank to the epoch number.  One NVLink traversal, no barrier, no further kernel.
+            __threadfence();
+            named_barrier(2, 256);
+            const int et = q * 128 + wq * 32 + lane;  // 0 .. 255
+            if (et == 0) {
+                unsigned *ticket = p.tp_flags[p.tp_rank] + 17;
+                const unsigned old = atomicAdd(ticket, 1u);
+                const int last = old == gridDim.x - 1;
+                if (last) *ticket = 0;
+                flags[1] = last;
+            }
+            named_barrier(2, 256);
+            if (flags[1] != 0) {
+                __threadfence();
+                const long long n4 = p.tp_count / 4;
+                const long long slot_off = (static_cast<long long>(tp_epoch & 1u) * p.tp_world + p.tp_rank) * p.tp_count;
+                for (long long i = et; i < n4; i += 256) {
+                    const float4 v = __ldcg(reinterpret_cast<const float4 *>(tp_slot_mine) + i);
+                    for (int r = 0; r < p.tp_world; ++r)
+                        if (r != p.tp_rank) reinterpret_cast<float4 *>(p.peer_out[r] + slot_off)[i] = v;
+                }
+                __threadfence_system();
+                named_barrier(2, 256);
+                if (et < p.tp_world)
+                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.tp_flags[et] + p.tp_rank), "r"(tp_epoch) : "memory");
+                if (et == 0) {
+                    __threadfence();
+                    *reinterpret_cast<volatile unsigned *>(p.tp_flags[p.tp_rank] + 16) = tp_epoch;  // the epoch counter moves on
+                }
+            }
+            named_barrier(2, 256);
         }
         if (n_ops > 1 && q < 2) {
             // Chain: tell the other CTAs that this one has finished op `op` (all its atomic adds
@@ -1157,6 +1291,17 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
                  i += static_cast<long long>(gridDim.x) * ZT)
                 p.zero_ptr[i] = 0.f;
         }
+        if (kTp && p.tp_mode == 2) {
+            // producer of epoch e + 1 (counter = e now that the previous kernel has finished): this rank's own
+            // slot of parity e & 1 was read for the last time by the consumer before this kernel; clear it
+            // for epoch e + 2
+            constexpr int ZT = kULoadWarps * 32;
+            const unsigned e = *reinterpret_cast<volatile const unsigned *>(p.tp_flags[p.tp_rank] + 16);
+            float *z = p.peer_out[p.tp_rank] + (static_cast<long long>(e & 1u) * p.tp_world + p.tp_rank) * p.tp_count;
+            for (long long i = static_cast<long long>(cta) * ZT + wl * 32 + lane; i < p.tp_count;
+                 i += static_cast<long long>(gridDim.x) * ZT)
+                z[i] = 0.f;
+        }
         if (kTp && p.move_count > 0) {
             constexpr int ZT = kULoadWarps * 32;
             for (long long i = static_cast<long long>(cta) * ZT + wl * 32 + lane; i < p.move_count;
@@ -1172,6 +1317,29 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
             __threadfence();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(Plan::kBarGridOk));
+        }
+        // Tensor-parallel consumer: wait (bounded) until every rank has pushed the partial product of the
+        // row-parallel layer before this one -- epoch = this rank's counter, moved on by that layer's kernel,
+        // which has finished -- then read the activations as residual + all slots of that epoch's parity.
+        [[maybe_unused]] const float *tp_slots_now = nullptr;
+        if (kTp && p.tp_mode == 3) {
+            const unsigned e = *reinterpret_cast<volatile const unsigned *>(p.tp_flags[p.tp_rank] + 16);
+            if (lane < p.tp_world) {
+                const unsigned *mine = p.tp_flags[p.tp_rank] + lane;
+                const long long t0 = clock64();
+                for (;;) {
+                    unsigned v;
+                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+                    if (static_cast<int>(v - e) >= 0) break;
+                    if (clock64() - t0 > p.tp_wait) {
+                        raise_status(DMM_STATUS_WAIT_TIMEOUT);
+                        break;
+                    }
+                    __nanosleep(40);
+                }
+            }
+            __syncwarp();
+            tp_slots_now = p.peer_out[p.tp_rank] + static_cast<long long>(e & 1u) * p.tp_world * p.tp_count;
         }
         [[maybe_unused]] const __half *x = reinterpret_cast<const __half *>(p.x);
         const int M = static_cast<int>(p.M);
@@ -1271,7 +1439,11 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
                             const int kt = gt - (gt / KT) * KT;
                             const long long k0 = 32ll * kt + 8 * kc;
                             dst[u] = ebuf + jl * tile_b + (kc >> 1) * (tile_b / 2) + row * 16 + (kc & 1) * 8;
-                            load_piece(p.x, p.x_mode, p.x_ld, p.x_gap, row, k0, h[u]);
+                            if (kTp && p.tp_mode == 3)
+                                load_piece_sum(reinterpret_cast<const float *>(p.x), p.h_out, tp_slots_now, p.tp_world, p.tp_count, p.x_ld,
+                                               row, k0, h[u]);
+                            else
+                                load_piece(p.x, p.x_mode, p.x_ld, p.x_gap, row, k0, h[u]);
                         }
                     }
 #pragma unroll
@@ -1409,13 +1581,13 @@ inline int launch_umma_ops(const UmmaParams *ops, int n_ops, unsigned *sync, int
     // four TMA producer warps up to two batch rows of the fp16 family (measured 1 % faster at batch 1), else one
     bool split = false;
     if constexpr (Pol::kIsF8 && !kChain) {  // tensor-parallel epilogue: its own instantiation, nothing of it in the plain kernel
-        if (ops[0].n_peers > 0 || ops[0].move_count > 0) kernel = umma_kernel<Pol, NMMA, kChain, true>;
+        if (ops[0].n_peers > 0 || ops[0].move_count > 0 || ops[0].tp_mode != 0) kernel = umma_kernel<Pol, NMMA, kChain, true>;
     }
     if constexpr (Pol::kIsF8 && !Pol::kIsInt && !kChain && NMMA == 32) {
         if (ops[0].M <= 2) {
             split = true;
             kernel = umma_kernel<Pol, NMMA, kChain, false, true>;
-            if (ops[0].n_peers > 0 || ops[0].move_count > 0) kernel = umma_kernel<Pol, NMMA, kChain, true, true>;
+            if (ops[0].n_peers > 0 || ops[0].move_count > 0 || ops[0].tp_mode != 0) kernel = umma_kernel<Pol, NMMA, kChain, true, true>;
         }
     }
     cudaError_t err =

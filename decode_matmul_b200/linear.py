@@ -70,8 +70,10 @@ class LinearStack:
     what the tensor-parallel tests compare.  Meant for small configurations."""
 
     def __init__(self, cfg: dict, codebook_fp16: torch.Tensor, device, world: int = 1, rank: int = 0,
-                 seed: int = 46, scale: float = 2.0 ** -7, group=None, logical_seed: int | None = None):
+                 seed: int = 46, scale: float = 2.0 ** -7, group=None, logical_seed: int | None = None,
+                 tp_mode: str | None = None):
         self.cfg, self.world, self.rank, self.group = cfg, world, rank, group
+        self.tp_mode = tp_mode  # None: by rank count and DMM_TP_MODE; "slots" | "pull" | "push" | "nccl"
         self.device = torch.device(device)
         self.hidden, self.ffn = cfg["hidden"], cfg["ffn"]
         shapes = llama_shapes(cfg["hidden"], cfg["kv_heads"], cfg["head_dim"], cfg["ffn"])
@@ -162,8 +164,17 @@ class LinearStack:
         if getattr(self, "_peer_key", None) == key:
             return self._peer
         self._peer_key, self._peer = key, None
-        if self.world == 1 or os.environ.get("DMM_TP_PEER", "1") == "0":
+        if self.world == 1 and self.tp_mode == "slots":
+            # a group of one: the same kernels on ordinary local buffers (what the one-GPU tests run)
+            slots = torch.zeros((2, 1, batch, self.hidden), dtype=torch.float32, device=self.device)
+            sflags = torch.zeros((64,), dtype=torch.int32, device=self.device)
+            self._peer = dict(slots=slots, sflags=sflags, slot_ptrs=[slots.data_ptr()], sflag_ptrs=[sflags.data_ptr()],
+                              h2=torch.zeros((2, batch, self.hidden), dtype=torch.float32, device=self.device))
+            return self._peer
+        if self.world == 1 or os.environ.get("DMM_TP_PEER", "1") == "0" or self.tp_mode == "nccl":
             return None
+        # the kernels use plain peer loads and stores only: keep the buffers off NVLink multicast objects
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         ok = torch.zeros(1, device=self.device)
         try:
             import torch.distributed._symmetric_memory as symm
@@ -171,13 +182,19 @@ class LinearStack:
             group = self.group if self.group is not None else torch.distributed.group.WORLD
             res = symm.empty((2, batch, self.hidden), dtype=torch.float32, device=self.device)
             flags = symm.empty((64,), dtype=torch.int32, device=self.device)
-            res.zero_()
-            flags.zero_()
+            slots = symm.empty((2, self.world, batch, self.hidden), dtype=torch.float32, device=self.device)
+            sflags = symm.empty((64,), dtype=torch.int32, device=self.device)
+            for t in (res, flags, slots, sflags):
+                t.zero_()
             h_res, h_flags = symm.rendezvous(res, group), symm.rendezvous(flags, group)
+            h_slots, h_sflags = symm.rendezvous(slots, group), symm.rendezvous(sflags, group)
             nbytes = batch * self.hidden * 4
             peer = dict(res=res, flags=flags, cur=0, mode=os.environ.get("DMM_TP_MODE", "pull"),
                         res_ptrs=[[int(ptr) + i * nbytes for ptr in h_res.buffer_ptrs] for i in range(2)],
-                        flag_ptrs=[int(ptr) for ptr in h_flags.buffer_ptrs])
+                        flag_ptrs=[int(ptr) for ptr in h_flags.buffer_ptrs],
+                        slots=slots, sflags=sflags, slot_ptrs=[int(ptr) for ptr in h_slots.buffer_ptrs],
+                        sflag_ptrs=[int(ptr) for ptr in h_sflags.buffer_ptrs],
+                        h2=torch.zeros((2, batch, self.hidden), dtype=torch.float32, device=self.device))
             ok.fill_(1)
         except Exception:  # no peer mapping on this system: every rank must fall back together
             peer = None
@@ -218,6 +235,46 @@ class LinearStack:
             cur = 1 - cur
         h.copy_(res[cur])
         res[cur].zero_()  # restores the starting state: both buffers zero, so `cur` may restart at 0
+        return h
+
+    def _step_fused_slots(self, h: torch.Tensor, peer) -> torch.Tensor:
+        """Tensor-parallel fused step with compute and collective in the matmul kernels: a row-parallel
+        kernel's last CTA copies the finished partial product into this rank's slot on every rank and
+        raises a flag; the loaders of the column-parallel kernel that follows wait for all ranks' flags and
+        read the residual stream plus all slots (writing the sum back as the new residual stream).  One
+        NVLink traversal per row-parallel layer, no barrier, no reduction kernel; four launches per block
+        as on one GPU.  The residual stream alternates between two local buffers."""
+        from . import ops as _ops
+
+        B = h.shape[0]
+        buf = self._buffers(B)
+        a, g = buf["a"], buf["g"]
+        hid_loc, ffn_loc = self.hidden // self.world, self.ffn // self.world
+        h2, slots, sflags = peer["h2"], peer["slots"], peer["sflags"]
+        sp, fp, w, r = peer["slot_ptrs"], peer["sflag_ptrs"], self.world, self.rank
+        cur = 0
+        h2[cur].copy_(h)
+        a.zero_()
+        kw = dict(accumulate=True, atomic=True, pdl=True)
+        mm, hint = _ops.decode_matmul_fused, _ops.hint_next_weights
+        for i, blk in enumerate(self.layers):
+            q, o, gu, dn = blk["qkv"], blk["o"], blk["gate_up"], blk["down"]
+            nxt = self.layers[i + 1]["qkv"].codes if i + 1 < len(self.layers) else None
+            hint(o.codes)
+            if i == 0:  # nothing pending from a row-parallel layer yet
+                mm(h2[cur], q.codes, q.codebook, q.scale, a, x_kind=_lib.X_F32, zero=g, **kw)
+            else:       # the partial products of the previous block's down projection arrive through the slots
+                _ops.tp_consume(h2[cur], h2[1 - cur], slots, sflags, w, q.codes, q.codebook, q.scale, a, pdl=True, zero=g)
+                cur = 1 - cur
+            hint(gu.codes)
+            _ops.tp_produce(a, o.codes, o.codebook, o.scale, sp, fp, r, self.hidden, x_kind=_lib.X_F32, pdl=True)
+            hint(dn.codes)
+            _ops.tp_consume(h2[cur], h2[1 - cur], slots, sflags, w, gu.codes, gu.codebook, gu.scale, g, pdl=True, zero=a)
+            cur = 1 - cur
+            hint(nxt)
+            _ops.tp_produce(g, dn.codes, dn.codebook, dn.scale, sp, fp, r, self.hidden, x_kind=_lib.X_F32_SILU_MUL,
+                            x_gap=ffn_loc, pdl=True)
+        _ops.tp_finalize(h2[cur], h, slots, sflags, w)
         return h
 
     def _step_fused_pull(self, h: torch.Tensor, peer) -> torch.Tensor:
@@ -262,14 +319,19 @@ class LinearStack:
     def _step_fused(self, h: torch.Tensor) -> torch.Tensor:
         from .ops import decode_matmul_fused as mm
 
-        if self.world > 1 and h.shape[0] <= 32:
+        if (self.world > 1 or self.tp_mode == "slots") and h.shape[0] <= 32:
             import os
 
             peer = self._peer_state(h.shape[0])
             if peer is not None:
-                # measured on B200 (ms per step at batch 1): pull 5.36 / 4.84 / 5.63 and push 5.67 / - / 5.37
-                # at 2 / 4 / 8 ranks
-                mode = os.environ.get("DMM_TP_MODE", "pull" if self.world <= 4 else "push")
+                # measured on B200, ms per step at batch 1, 2 ranks: pull 5.39, slots 5.93 (the copy to the peers by
+                # the producer's last CTA and the ticket all CTAs pass cost more than the small kernel they
+                # replace); earlier: pull 5.36 / 4.84 / 5.63 and push 5.67 / - / 5.37 at 2 / 4 / 8 ranks
+                mode = self.tp_mode or os.environ.get("DMM_TP_MODE", "pull" if self.world <= 4 else "push")
+                if mode == "slots" and h.shape[0] > 8:
+                    mode = "pull"  # the slots form splits the activations inside the kernel: small batches only
+                if mode == "slots":
+                    return self._step_fused_slots(h, peer)
                 if mode == "push":
                     return self._step_fused_peer(h, peer)
                 return self._step_fused_pull(h, peer)

@@ -158,6 +158,62 @@ def decode_matmul_fused_tp(x, weights_compressed, codebook_fp16, scale, peer_out
     _lib.check(rc, "decode_matmul_fused_tp")
 
 
+def tp_produce(x, weights_compressed, codebook_fp16, scale, peer_slot_ptrs, peer_flag_ptrs, rank, out_features, *,
+               x_kind=_lib.X_F32, x_gap=0, sign_convention=_lib.SIGN_SLOW, pdl=False):
+    """Row-parallel product of a tensor-parallel step in the slots form (``dmm_f16_tp_produce``): the partial
+    product goes into this rank's slot on every rank (``peer_slot_ptrs`` / ``peer_flag_ptrs``: device addresses
+    of every rank's slot array and flag words, this rank's own at index ``rank``)."""
+    _check_input(x, "x", torch.float16 if x_kind == _lib.X_F16 else torch.float32)
+    _check_input(weights_compressed, "weights_compressed", torch.int16)
+    _check_input(codebook_fp16, "codebook_fp16", torch.float16)
+    M, ld = x.shape
+    N, K = weights_compressed.size(0), weights_compressed.size(1) * 8
+    _req(N == out_features, "weights_compressed has the wrong number of rows")
+    world = len(peer_slot_ptrs)
+    slots = (ctypes.c_void_p * world)(*[int(v) for v in peer_slot_ptrs])
+    flg = (ctypes.c_void_p * world)(*[int(v) for v in peer_flag_ptrs])
+    with torch.cuda.device(x.device):
+        rc = _lib.lib().dmm_f16_tp_produce(_ptr(x), x_kind, ld, x_gap, _ptr(weights_compressed), _ptr(codebook_fp16),
+                                           float(scale), slots, flg, rank, world, M, N, K, sign_convention,
+                                           _lib.FLAG_PDL if pdl else 0, _stream_ptr(x.device))
+    _lib.check(rc, "tp_produce")
+
+
+def tp_consume(h_in, h_out, slots, flags, world, weights_compressed, codebook_fp16, scale, output, *,
+               sign_convention=_lib.SIGN_SLOW, pdl=False, zero=None):
+    """Column-parallel product whose loaders read ``h_in`` + the partial products that all ranks pushed into this
+    rank's ``slots`` (``dmm_f16_tp_consume``); the summed residual stream is written to ``h_out``."""
+    _check_input(h_in, "h_in", torch.float32)
+    _check_input(h_out, "h_out", torch.float32)
+    _check_input(slots, "slots", torch.float32)
+    _check_input(weights_compressed, "weights_compressed", torch.int16)
+    _check_input(codebook_fp16, "codebook_fp16", torch.float16)
+    _check_input(output, "output", torch.float32)
+    _req(h_in.shape == h_out.shape and h_in.data_ptr() != h_out.data_ptr(), "h_out must be another buffer of h_in's shape")
+    M, ld = h_in.shape
+    N, K = weights_compressed.size(0), weights_compressed.size(1) * 8
+    _req(tuple(output.shape) == (M, N), "output must have shape [M, N]")
+    _req(slots.numel() == 2 * world * M * K, "slots must hold [2][world][M * K] floats")
+    if zero is not None:
+        _check_input(zero, "zero", torch.float32)
+    with torch.cuda.device(h_in.device):
+        rc = _lib.lib().dmm_f16_tp_consume(_ptr(h_in), _ptr(h_out), ld, _ptr(slots), _ptr(flags), world, M * K,
+                                           _ptr(weights_compressed), _ptr(codebook_fp16), float(scale), _ptr(output), M, N, K,
+                                           sign_convention, _lib.FLAG_PDL if pdl else 0, None if zero is None else _ptr(zero),
+                                           0 if zero is None else zero.numel(), _stream_ptr(h_in.device))
+    _lib.check(rc, "tp_consume")
+
+
+def tp_finalize(h_in, h_out, slots, flags, world):
+    """``h_out = h_in + the slots of the last epoch`` (``dmm_tp_finalize``)."""
+    _check_input(h_in, "h_in", torch.float32)
+    _check_input(h_out, "h_out", torch.float32)
+    with torch.cuda.device(h_in.device):
+        rc = _lib.lib().dmm_tp_finalize(_ptr(h_in), _ptr(h_out), _ptr(slots), _ptr(flags), world, h_in.numel(),
+                                        _stream_ptr(h_in.device))
+    _lib.check(rc, "tp_finalize")
+
+
 def xrank_barrier(peer_flag_ptrs, rank, device):
     """Barrier kernel between the ranks of a tensor-parallel group (``dmm_xrank_barrier``)."""
     ptrs = (ctypes.c_void_p * len(peer_flag_ptrs))(*[int(v) for v in peer_flag_ptrs])

@@ -154,6 +154,40 @@ int dmm_f16_fused_tp(const void *x, int x_kind, int64_t x_ld, int64_t x_gap, con
                      int64_t zero_count, float *move_src, float *move_dst, int64_t move_count, void *stream);
 
 /*
+ * Tensor-parallel step in the "slots" form: compute and collective in the matmul kernels themselves, one
+ * NVLink traversal per row-parallel layer, no barrier and no separate reduction kernel.  (No counterpart
+ * in the reference.)
+ *
+ * Every rank owns a slot array, float [2 parities][world][count] with count = M * N of the row-parallel
+ * products, and `world` flag words followed by private words (at least 32 uint32 in all), both zero at the
+ * start and both mapped on every rank (peer_slots[r], peer_flags[r]: the arrays of rank r; entry [rank] is
+ * this rank's own).  Row-parallel layers are numbered by an epoch counter that the library keeps in the
+ * flag array.
+ *
+ * dmm_f16_tp_produce: a row-parallel product.  The kernel accumulates the partial product into this rank's
+ * own slot of the epoch's parity; the last CTA to finish copies the finished partial into this rank's slot
+ * on every other rank with plain vector stores (one value per element and peer) and then raises this
+ * rank's flag on every rank to the epoch number.  It also clears the own slot of the other parity.
+ * dmm_f16_tp_consume: the column-parallel product that follows.  Its activation loaders wait, bounded
+ * (DMM_STATUS_WAIT_TIMEOUT, dmm_set_wait_limit_ms), until the flags of all ranks show the epoch, and read
+ * the activations as h_in + the slots of all ranks, summed in rank order (every rank gets the same bits);
+ * the sum, the new residual stream, is also written to h_out ([M, K] fp32 like h_in; another buffer than
+ * h_in).  Result: out (+)= scale * fp16(h_out) . W^T with atomic adds, as dmm_f16_fused with DMM_X_F32.
+ * dmm_tp_finalize: h_out = h_in + slots of the last epoch, as a small kernel (end of a step).
+ * Batch M <= 8.  flags: DMM_FLAG_PDL only.  Two slot parities suffice: a rank can start epoch e + 2 only
+ * after every rank has finished reading epoch e.
+ */
+int dmm_f16_tp_produce(const void *x, int x_kind, int64_t x_ld, int64_t x_gap, const int16_t *codes, const void *cb16,
+                       float scale, float *const *peer_slots, unsigned *const *peer_flags, int rank, int world,
+                       int64_t M, int64_t N, int64_t K, int sign_convention, unsigned flags, void *stream);
+int dmm_f16_tp_consume(const float *h_in, float *h_out, int64_t x_ld, const float *slots, const unsigned *flags_local,
+                       int world, int64_t slot_count, const int16_t *codes, const void *cb16, float scale, float *out,
+                       int64_t M, int64_t N, int64_t K, int sign_convention, unsigned flags, float *zero_ptr,
+                       int64_t zero_count, void *stream);
+int dmm_tp_finalize(const float *h_in, float *h_out, const float *slots, const unsigned *flags_local, int world,
+                    int64_t count, void *stream);
+
+/*
  * Barrier between the ranks of a tensor-parallel group, as a kernel on `stream`: returns (on the
  * device) once every rank has enqueued and reached the same barrier, which also makes the peer
  * adds of the dmm_f16_fused_tp calls before it visible.  peer_flags[r] (r < world <= 8) point to

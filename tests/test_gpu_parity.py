@@ -459,24 +459,22 @@ for B in (1, 5):
     # the same LOGICAL weights on every rank count: the unsharded model on this GPU is the reference
     whole = LinearStack(cfg, cb, dev, world=1, rank=0, logical_seed=9, scale=sc)
     want = whole.step(h0.clone(), fused=True)
-    stack = LinearStack(cfg, cb, dev, world=world, rank=rank, logical_seed=9, scale=sc)
-    peer = stack._peer_state(B)
-    outs = {"pull": [stack.step(h0.clone(), fused=True) for _ in range(3)]}   # one-shot all-reduce kernel
-    os.environ["DMM_TP_MODE"] = "push"
-    push = LinearStack(cfg, cb, dev, world=world, rank=rank, logical_seed=9, scale=sc)
-    outs["push"] = [push.step(h0.clone(), fused=True) for _ in range(3)]      # epilogues add into every rank's buffer
-    os.environ["DMM_TP_MODE"] = "pull"
-    os.environ["DMM_TP_PEER"] = "0"
-    nccl = LinearStack(cfg, cb, dev, world=world, rank=rank, logical_seed=9, scale=sc)
-    outs["nccl"] = [nccl.step(h0.clone(), fused=True)]
-    os.environ["DMM_TP_PEER"] = "1"
+    outs, peer_ok = {}, True
+    for mode in ("slots", "pull", "push", "nccl"):
+        st = LinearStack(cfg, cb, dev, world=world, rank=rank, logical_seed=9, scale=sc, tp_mode=mode)
+        if mode != "nccl":
+            peer_ok = peer_ok and st._peer_state(B) is not None
+        outs[mode] = [st.step(h0.clone(), fused=True) for _ in range(3 if mode != "nccl" else 1)]
+        torch.cuda.synchronize()
+        del st
+    peer = True if peer_ok else None
     torch.cuda.synchronize()
     tol = 2e-3 * max(1.0, float(want.abs().max()))
     for mode, hs in outs.items():
         err = max(float((h - want).abs().max()) for h in hs)
         ok = ok and err <= tol
         print(f"rank {rank} B={B} world={world} {mode} vs world=1: max abs diff {err:.3e} (tol {tol:.1e})", flush=True)
-    # one block against the CPU oracle, sharded over the ranks (pull form) and unsharded
+    # one block against the CPU oracle, sharded over the ranks (default form: slots) and unsharded
     cfg1 = dict(cfg, layers=1)
     one = LinearStack(cfg1, cb, dev, world=1, rank=0, logical_seed=9, scale=sc)
     one_tp = LinearStack(cfg1, cb, dev, world=world, rank=rank, logical_seed=9, scale=sc)
@@ -485,7 +483,7 @@ for B in (1, 5):
     e2 = float(np.abs(one_tp.step(h0.clone(), fused=True).cpu().numpy() - ref).max())
     ok = ok and peer is not None and e1 <= 2e-3 and e2 <= 2e-3 and dmm.status() == 0
     print(f"rank {rank} B={B} one block vs oracle: world=1 {e1:.3e}, world={world} {e2:.3e}, peer memory {peer is not None}", flush=True)
-    del stack, push, nccl, one_tp
+    del one_tp
 dist.barrier(); torch.cuda.synchronize()
 print("TP_OK" if ok else "TP_FAIL", flush=True)
 sys.stdout.flush()
@@ -496,8 +494,9 @@ os._exit(0 if ok else 1)
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_tensor_parallel_step_matches_one_gpu_and_oracle(tmp_path):
     """Two ranks (one process per GPU) share ONE set of logical weights (LinearStack logical_seed): the
-    fused step summed over the ranks by the one-shot all-reduce kernel (pull), by epilogues that add
-    into every rank's residual buffer (push) and by NCCL all-reduce must each equal the step of the
+    fused step in its four forms -- partial products pushed into per-rank slots and summed by the next
+    kernel's loaders (slots, the default), one-shot all-reduce kernel (pull), epilogues that add into every
+    rank's residual buffer (push), NCCL all-reduce -- must each equal the step of the
     unsharded model on one GPU, and one block must equal the CPU oracle.  NVLS is off (a rank that
     died while its memory was bound to an NVLink group object has faulted its peers on shared hosts)."""
     import subprocess
@@ -513,3 +512,23 @@ def test_tensor_parallel_step_matches_one_gpu_and_oracle(tmp_path):
     print(res.stdout[-3000:])
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-2000:]
     assert res.stdout.count("TP_OK") == 2
+
+
+@pytest.mark.parametrize("batch", [1, 3])
+def test_slots_form_of_the_tensor_parallel_step_on_one_gpu(batch):
+    """The slots form of the tensor-parallel step (dmm_f16_tp_produce / _consume / dmm_tp_finalize) in a
+    group of one: same kernels, epochs, slot parities and clearing as across GPUs, only no peer to copy to.
+    Three steps in a row (the epoch counter and the slot parities carry over) against the plain fused step."""
+    from decode_matmul_b200.linear import LinearStack
+
+    cfg = dict(hidden=512, kv_heads=2, head_dim=64, ffn=1024, layers=3)
+    cb = dmm.synthetic_codebook(42)
+    plain = LinearStack(cfg, cb, "cuda", logical_seed=12, scale=2.0 ** -8)
+    slots = LinearStack(cfg, cb, "cuda", logical_seed=12, scale=2.0 ** -8, tp_mode="slots")
+    torch.manual_seed(batch)
+    for step in range(3):
+        h0 = torch.randn(batch, 512, device="cuda")
+        want = plain.step(h0.clone(), fused=True)
+        got = slots.step(h0.clone(), fused=True)
+        assert dmm.status() == 0
+        assert torch.allclose(got, want, rtol=2e-3, atol=2e-3), f"step {step}: {float((got - want).abs().max())}"

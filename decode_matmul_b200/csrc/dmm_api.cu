@@ -123,13 +123,16 @@ static int retile_fast(DeviceState *d, const void *codes, long long N, long long
     {
         std::lock_guard<std::mutex> lock(g_mutex);
         if (d->retile_bytes < need) {
-            cudaError_t err = cudaDeviceSynchronize();  // earlier calls may still read the old buffer
+            // as for the workspace: no allocation under stream capture, and an outgrown buffer is parked,
+            // never freed (work already enqueued and graphs captured earlier keep using it)
+            cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+            cudaError_t err = cudaStreamIsCapturing(stream, &cap);
             if (err != cudaSuccess) return err;
-            if (d->retile) cudaFree(d->retile);
-            d->retile = nullptr;
-            d->retile_bytes = 0;
-            err = cudaMalloc(&d->retile, need);
+            if (cap != cudaStreamCaptureStatusNone) return DMM_ERR_WORKSPACE;
+            void *fresh = nullptr;
+            err = cudaMalloc(&fresh, need);
             if (err != cudaSuccess) return err;
+            d->retile = fresh;
             d->retile_bytes = need;
         }
     }
@@ -208,7 +211,7 @@ struct TpArgs {
 static int run_umma(bool f8, const void *x, int x_kind, long long x_ld, long long x_gap, const void *codes,
                     const void *cb16, float scale, float *out, long long M, long long N, long long K,
                     int sign_convention, unsigned flags, void *workspace, size_t workspace_bytes, cudaStream_t stream,
-                    float *zero_ptr = nullptr, long long zero_count = 0, const TpArgs *tp = nullptr) {
+                    float *zero_ptr = nullptr, long long zero_count = 0, const TpArgs *tp = nullptr, bool fast_layout = false) {
     DeviceState *d = nullptr;
     int rc = current_device_state(&d);
     if (rc) return rc;
@@ -244,6 +247,7 @@ static int run_umma(bool f8, const void *x, int x_kind, long long x_ld, long lon
         p.accumulate = (flags & DMM_FLAG_ACCUMULATE) ? 1 : 0;
         p.atomic_reduce = (flags & DMM_FLAG_ATOMIC) ? 1 : 0;
         p.sign_convention = sign_convention;
+        p.fast_layout = fast_layout ? 1 : 0;
         if (m0 == 0) {
             p.zero_ptr = zero_ptr;
             p.zero_count = zero_count;
@@ -280,7 +284,7 @@ static int run_umma(bool f8, const void *x, int x_kind, long long x_ld, long lon
 #endif
         // 17 to 32 batch rows (128 MMA columns) run on the kernel of dmm_tc.cuh, measured faster there;
         // everything else on the kernel of dmm_umma.cuh
-        rc = (f8 && p.M > 16) ? launch_tc_wide(p, d->num_sms, pdl, stream) : launch_umma(f8, p, d->num_sms, pdl, stream);
+        rc = (f8 && p.M > 16 && !fast_layout) ? launch_tc_wide(p, d->num_sms, pdl, stream) : launch_umma(f8, p, d->num_sms, pdl, stream);
         g_launches.fetch_add(1, std::memory_order_relaxed);
         if (rc) return rc;
     }
@@ -290,7 +294,7 @@ static int run_umma(bool f8, const void *x, int x_kind, long long x_ld, long lon
 // Integer family on the tcgen05 kernel: one launch per chunk of 32 batch rows.
 static int run_umma_i8(const void *x, const void *codes, const void *cb64, int32_t *out, long long M, long long N,
                        long long K, int sign_convention, unsigned flags, void *workspace, size_t workspace_bytes,
-                       cudaStream_t stream) {
+                       cudaStream_t stream, bool fast_layout) {
     DeviceState *d = nullptr;
     int rc = current_device_state(&d);
     if (rc) return rc;
@@ -319,6 +323,7 @@ static int run_umma_i8(const void *x, const void *codes, const void *cb64, int32
         p.accumulate = 1;
         p.atomic_reduce = 1;
         p.sign_convention = sign_convention;
+        p.fast_layout = fast_layout ? 1 : 0;
 #ifdef DMM_TRACE
         p.trace = g_trace;
 #endif
@@ -371,16 +376,10 @@ int dmm_i8(const int8_t *x, const int16_t *codes, const int64_t *cb64, int32_t *
            int sign_convention, int layout, unsigned flags, void *workspace, size_t workspace_bytes, void *stream) {
     int rc = check_common(x, codes, cb64, out, M, N, K, sign_convention, layout);
     if (rc) return rc;
-    const void *tiled = codes;
-    if (layout == DMM_LAYOUT_FAST) {
-        DeviceState *d = nullptr;
-        rc = current_device_state(&d);
-        if (rc) return rc;
-        rc = retile_fast(d, codes, N, K, static_cast<cudaStream_t>(stream), &tiled);
-        if (rc) return rc;
-    }
-    return run_umma_i8(x, tiled, cb64, out, M, N, K, sign_convention, flags, workspace, workspace_bytes,
-                       static_cast<cudaStream_t>(stream));
+    // the tcgen05 kernel streams either layout as it lies in memory
+    if (layout == DMM_LAYOUT_FAST && N % 32 != 0) return DMM_ERR_SHAPE;
+    return run_umma_i8(x, codes, cb64, out, M, N, K, sign_convention, flags, workspace, workspace_bytes,
+                       static_cast<cudaStream_t>(stream), layout == DMM_LAYOUT_FAST);
 }
 
 int dmm_f16_fused(const void *x, int x_kind, int64_t x_ld, int64_t x_gap, const int16_t *codes, const void *cb16,
@@ -395,23 +394,29 @@ int dmm_f16_fused(const void *x, int x_kind, int64_t x_ld, int64_t x_gap, const 
     if (x_ld < K || x_ld % 8 != 0 || x_gap % 4 != 0 || (x_kind == DMM_X_F32_SILU_MUL && x_gap + K > x_ld))
         return DMM_ERR_SHAPE;
     if (zero_count < 0 || (zero_count > 0 && zero_ptr == nullptr)) return DMM_ERR_ARG;
-    if (layout == DMM_LAYOUT_FAST) {
-        DeviceState *d = nullptr;
-        rc = current_device_state(&d);
-        if (rc) return rc;
-        const void *tiled = nullptr;
-        rc = retile_fast(d, codes, N, K, static_cast<cudaStream_t>(stream), &tiled);
-        if (rc) return rc;
-        codes = reinterpret_cast<const int16_t *>(tiled);
-    }
     if (path == DMM_PATH_AUTO) path = x_kind == DMM_X_F16 ? dmm_select_path(M, N, K) : DMM_PATH_TCGEN05_F8;
+    bool fast_native = false;
+    if (layout == DMM_LAYOUT_FAST) {
+        if (N % 32 != 0) return DMM_ERR_SHAPE;
+        if (path == DMM_PATH_TCGEN05_F8) {
+            fast_native = true;  // streamed as it lies in memory
+        } else {                 // the cross-check paths read the tile layout: re-tile first (one extra pass)
+            DeviceState *d = nullptr;
+            rc = current_device_state(&d);
+            if (rc) return rc;
+            const void *tiled = nullptr;
+            rc = retile_fast(d, codes, N, K, static_cast<cudaStream_t>(stream), &tiled);
+            if (rc) return rc;
+            codes = reinterpret_cast<const int16_t *>(tiled);
+        }
+    }
     if (zero_count > 0 && path != DMM_PATH_TCGEN05 && path != DMM_PATH_TCGEN05_F8) return DMM_ERR_UNSUPPORTED;
     // fp32 inputs are converted by the loaders of the fp8-operand kernel only
     if (x_kind != DMM_X_F16 && path != DMM_PATH_TCGEN05_F8) return DMM_ERR_UNSUPPORTED;
     if (path == DMM_PATH_TCGEN05 || path == DMM_PATH_TCGEN05_F8)
         return run_umma(path == DMM_PATH_TCGEN05_F8, x, x_kind, x_ld, x_gap, codes, cb16, scale, out, M, N, K,
                         sign_convention, flags, workspace, workspace_bytes, static_cast<cudaStream_t>(stream), zero_ptr,
-                        zero_count);
+                        zero_count, nullptr, fast_native);
     if (x_ld != K) return DMM_ERR_UNSUPPORTED;
     // the streaming kernel accumulates quarter units: fold the 1/4 into the scale
     return run_stream(1, x, codes, cb16, 1, 0.25f * scale, out, M, N, K, sign_convention, flags, workspace,

@@ -168,6 +168,18 @@ __device__ __forceinline__ void sts64(uint32_t addr, uint32_t a, uint32_t b) {
     asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(addr), "r"(a), "r"(b) : "memory");
 }
 
+// The code words of one k-tile for a decoder thread, from a ring slot in the layout of fast_decode_matmul_cuda:
+// slot = [8 row blocks of 32][C k-tiles][2 code pairs][32 lanes] uint32, word = two consecutive codes of one
+// row.  The thread owns row `lane` of row block wq (MMA tile 0) and of row block wq + 4 (MMA tile 1); the
+// words are returned in the form the tile layout delivers them (low half: tile 0's row, high half: tile 1's
+// row, one word per code column), so that the decode that follows is the same for both layouts.
+__device__ __forceinline__ uint4 fetch_fast_ktile(uint32_t slot_addr, int c_tiles, int wq, int lane, int kt) {
+    const uint32_t a = slot_addr + static_cast<uint32_t>(wq * c_tiles + kt) * 256u + static_cast<uint32_t>(lane) * 4u;
+    const uint32_t b = a + static_cast<uint32_t>(4 * c_tiles) * 256u;
+    const uint32_t a0 = lds32(a), a1 = lds32(a + 128u), b0 = lds32(b), b1 = lds32(b + 128u);
+    return make_uint4(prmt(a0, b0, 0x5410u), prmt(a0, b0, 0x7632u), prmt(a1, b1, 0x5410u), prmt(a1, b1, 0x7632u));
+}
+
 // ----------------------------------- policies -----------------------------------------
 // kG  k-tiles per "group": the unit of decoder -> issuer hand-over (one barrier round trip,
 //     one tcgen05.commit).  Every tcgen05 instruction costs its issuing thread ~45-55 cycles
@@ -334,6 +346,7 @@ struct UmmaParams {
     // kernel's TMA producers have issued their last load they fetch, into L2 only, the first ring fill that
     // CTA `blockIdx.x` of that next launch will ask for, so that its first codes -- the longest wait of a
     // launch's prologue -- come from L2 instead of DRAM.
+    int fast_layout;     // codes are in the layout of fast_decode_matmul_cuda (fp8/int8 policies stream it natively)
     const void *next_codes;
     long long next_N, next_K;
     Part32 next_part;
@@ -799,6 +812,8 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
                 if (tid == 0) DMM_STAMP(5, cidx, 1);
                 // slot layout [16 strips][C k-tiles][128 B]; this lane: strip 4*wq + lane/8, piece lane%8
                 const uint32_t src = gring + slot * Plan::kSlotBytes + (wq * 4 + (lane >> 3)) * (C * 128) + (lane & 7) * 16;
+                const uint32_t fsrc = gring + slot * Plan::kSlotBytes;  // (fast layout: see fetch_fast_ktile)
+                const bool fast = Pol::kIsF8 && p0.fast_layout != 0;
 #pragma unroll 1
                 for (int g0 = 0; g0 < n; g0 += G) {
                     const int buf = static_cast<int>(sA % NA);
@@ -814,7 +829,7 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
 #pragma unroll
                         for (int i = 0; i < G; ++i) {
                             uint4 cw = make_uint4(0, 0, 0, 0);
-                            if (g0 + i < n) cw = lds128(src + (g0 + i) * 128);
+                            if (g0 + i < n) cw = fast ? fetch_fast_ktile(fsrc, C, wq, lane, g0 + i) : lds128(src + (g0 + i) * 128);
                             const uint32_t w[4] = {cw.x, cw.y, cw.z, cw.w};
 #pragma unroll
                             for (int t = 0; t < 4; ++t) {
@@ -924,7 +939,9 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
                 const bool full = len == KT;
                 const int my_slot = seg_kt0(ss) > 0 ? 0 : 1;
                 const int trow = wq * 32 + lane;  // TMEM lane = row of the MMA tile
-                const long long n = (static_cast<long long>(ss) * 16 + wq * 4 + (lane >> 3)) * 16 + 8 * q + (lane & 7);
+                const long long n = (Pol::kIsF8 && p.fast_layout != 0)
+                                        ? static_cast<long long>(ss) * 256 + 32 * (4 * q + wq) + lane
+                                        : (static_cast<long long>(ss) * 16 + wq * 4 + (lane >> 3)) * 16 + 8 * q + (lane & 7);
                 const int ptid = q * 128 + trow;
                 if (p.atomic_reduce) {
                     if (n < p.N) {
@@ -1210,7 +1227,7 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
                         if (n_q >= RING) mbar_wait(bar(Plan::kBarEmpty + q * RING + slot), par, flags);
                         const uint32_t b = bar(Plan::kBarCode + q * RING + slot);
                         mbar_arrive_expect_tx(b, Plan::kSlotBytes);
-                        tma_load_2d(ring_addr + (q * RING + slot) * Plan::kSlotBytes, &ch.map[0], (kt0 + c * C) * 32, ss * 16, b, policy);
+                        tma_load_2d(ring_addr + (q * RING + slot) * Plan::kSlotBytes, &ch.map[0], (kt0 + c * C) * (p.fast_layout ? 64 : 32), ss * (p.fast_layout ? 8 : 16), b, policy);
                         ++n_q;
                         if (++slot == RING) {
                             slot = 0;
@@ -1248,7 +1265,7 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
                         mbar_wait(bar(Plan::kBarEmpty + q * RING + slot), ((n_q / RING) - 1) & 1, flags);
                     const uint32_t b = bar(Plan::kBarCode + q * RING + slot);
                     mbar_arrive_expect_tx(b, Plan::kSlotBytes);
-                    tma_load_2d(ring_addr + (q * RING + slot) * Plan::kSlotBytes, &ch.map[op], (kt0 + c * C) * 32, ss * 16, b, policy);
+                    tma_load_2d(ring_addr + (q * RING + slot) * Plan::kSlotBytes, &ch.map[op], (kt0 + c * C) * (p.fast_layout ? 64 : 32), ss * (p.fast_layout ? 8 : 16), b, policy);
                     if (q == 0) ++cnt[0]; else if (q == 1) ++cnt[1]; else if (q == 2) ++cnt[2]; else ++cnt[3];
                 }
             }
@@ -1555,12 +1572,14 @@ inline EncodeTiledFn encode_tiled_fn() {
 }
 
 // Tensor map of the tiled code matrix seen as uint32 [strips][K/32 * 32], box = c_tiles k-tiles x 16 strips.
-inline int make_codes_map(CUtensorMap *map, const void *codes, long long N, long long K, int c_tiles) {
+// With `fast` the matrix is in the layout of fast_decode_matmul_cuda, seen as uint32 [row blocks of 32][K/16 * 32]:
+// a k-tile of a row block is 64 consecutive words, box = c_tiles k-tiles x 8 row blocks (the same 8 KiB).
+inline int make_codes_map(CUtensorMap *map, const void *codes, long long N, long long K, int c_tiles, bool fast = false) {
     EncodeTiledFn fn = encode_tiled_fn();
     if (fn == nullptr) return cudaErrorNotSupported;
-    const cuuint64_t gdim[2] = {static_cast<cuuint64_t>(K), static_cast<cuuint64_t>(N / 16)};  // K/32 tiles x 32 words
-    const cuuint64_t gstride[1] = {static_cast<cuuint64_t>(K) * 4};                               // bytes per strip
-    const cuuint32_t box[2] = {static_cast<cuuint32_t>(c_tiles * 32), 16};
+    const cuuint64_t gdim[2] = {static_cast<cuuint64_t>(fast ? 2 * K : K), static_cast<cuuint64_t>(fast ? N / 32 : N / 16)};
+    const cuuint64_t gstride[1] = {static_cast<cuuint64_t>(K) * (fast ? 8 : 4)};  // bytes per strip / row block
+    const cuuint32_t box[2] = {static_cast<cuuint32_t>(c_tiles * (fast ? 64 : 32)), static_cast<cuuint32_t>(fast ? 8 : 16)};
     const cuuint32_t estride[2] = {1, 1};
     const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void *>(codes), gdim, gstride, box, estride,
                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
@@ -1621,7 +1640,8 @@ inline int launch_umma_ops(const UmmaParams *ops, int n_ops, unsigned *sync, int
                 p.next_part.b = static_cast<int>(Tn % gn);
             }
         }
-        const int rc = make_codes_map(&ch.map[i], p.codes, p.N, p.K, Pol::kC);
+        if (p.fast_layout) p.next_codes = nullptr;  // (the prefetch hint describes the tile layout)
+        const int rc = make_codes_map(&ch.map[i], p.codes, p.N, p.K, Pol::kC, Pol::kIsF8 && p.fast_layout != 0);
         if (rc) return rc;
     }
     cudaLaunchConfig_t cfg = {};

@@ -112,3 +112,36 @@ def test_accumulation_error_at_the_longest_reduction(oracle_c):
     err, rel = _check(y, want, "K = 28672")
     print(f"K=28672: max |y| {np.abs(want).max():.1f}, max abs err {err:.3e}, rel L2 {rel:.3e}")
     assert err <= 1e-5 * np.abs(want).max()
+
+
+def test_fast_layout_streams_natively_on_a_benchmark_shape(oracle_c):
+    """fast_decode_matmul_cuda.decode_matmul (fast layout, that file's sign convention, in-place accumulate)
+    at 8 x 28672 x 8192: the tcgen05 kernel reads the fast layout as it lies in memory (no re-tiling pass);
+    exact against the oracle, and the same codes converted to the other convention and the tile layout
+    give the same integers through decode_matmul_cuda."""
+    import decode_matmul_cuda as slow
+    import fast_decode_matmul_cuda as fast
+
+    M, N, K = 8, 28672, 8192
+    rng = np.random.default_rng(99)
+    codes = rng.integers(-32768, 32768, size=(N, K // 8), dtype=np.int16)
+    x = rng.integers(-128, 128, size=(M, K), dtype=np.int8)
+    cb64 = np.ascontiguousarray(o.golden_codebook_abs())
+    want = np.empty((M, N), np.int32)
+    oracle_c.oracle_matmul_i8(_p(x), _p(codes), _p(cb64), 1, ctypes.c_int64(M), ctypes.c_int64(N), ctypes.c_int64(K), _p(want))
+    launches = dmm.launch_count()
+    out = torch.zeros((M, N), dtype=torch.int32, device="cuda")
+    got = fast.decode_matmul(_dev(x), _dev(o.fast_pack(codes)), _dev(cb64), out)
+    assert dmm.launch_count() == launches + 1, "one kernel: no re-tiling pass"
+    assert np.array_equal(got.cpu().numpy(), want)
+    # the converter: the same weights in the other convention and layout
+    slow_codes = dmm.convert_sign_convention(torch.from_numpy(codes), dmm.SIGN_FAST, dmm.SIGN_SLOW)
+    y = slow.decode_matmul(_dev(x), dmm.transpose_tile(slow_codes).cuda(), _dev(cb64))
+    assert np.array_equal(y.cpu().numpy(), want)
+    # fp16 family on the fast layout, batch 1 and 20 (the wide variant)
+    cb16 = o.synthetic_codebook(42)
+    for B in (1, 20):
+        xh = rng.standard_normal((B, K)).astype(np.float16)
+        yh = dmm.decode_matmul_fp16(_dev(xh), _dev(o.fast_pack(codes)), _dev(cb16), 1.0, layout=dmm.LAYOUT_FAST).cpu().numpy()
+        _check(yh, _oracle_f16(oracle_c, xh, codes, cb16, 1.0), f"fp16 fast layout batch {B}")
+    assert dmm.status() == 0

@@ -47,6 +47,12 @@ def parse():
     ap.add_argument("--layers", type=int, default=80)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-shapes", action="store_true", help="skip the per-shape table and the batch-32 line (N = 1 only)")
+    ap.add_argument("--shape", default=None, metavar="FAMILY:B:N:K",
+                    help="instead of the stack: one product, e.g. fp16:1:57344:8192 or int8:8:28672:8192; runs it "
+                         "--calls times (the smallest driver for a profiler) or, with --time, times it")
+    ap.add_argument("--calls", type=int, default=3)
+    ap.add_argument("--path", type=int, default=0, help="with --shape (fp16 family): DMM_PATH_* value, 0 = auto")
+    ap.add_argument("--time", action="store_true")
     return ap.parse_args()
 
 
@@ -479,8 +485,16 @@ def run_ours(args):
         line.update(extra)
         print(json.dumps(line), flush=True)
     if world > 1:
-        # Captured graphs hold NCCL work; tearing the process group down under them can block.
-        # Everything is measured and printed: leave together and skip the teardown.
+        # Leave together.  The captured graphs hold kernels that spin on peer flags (and, in the NCCL form,
+        # collectives): destroy them and every peer-mapped buffer first, drain the device, then skip the
+        # process-group teardown -- destroy_process_group with graphs of its collectives alive blocked here for
+        # the whole time limit, and a rank must not exit while a peer can still touch its memory.
+        try:
+            del graph, graph_e2e, kgraph
+        except NameError:
+            pass
+        stack._peer = None
+        torch.cuda.synchronize()
         dist.barrier()
         torch.cuda.synchronize()
         sys.stdout.flush()
@@ -488,8 +502,38 @@ def run_ours(args):
         os._exit(0)
 
 
+def run_shape(args):
+    """One product on cuda:0: a few plain calls (random codes, the synthetic {0.5..3.5} codebook for the fp16 family,
+    the E8P table for the integer family; prints the device status word and a checksum), or one timing line."""
+    import torch
+
+    import decode_matmul_b200 as dmm
+
+    family, b, n, k = args.shape.split(":")
+    b, n, k = int(b), int(n), int(k)
+    if args.time:
+        print(json.dumps(dict(time_shape(dmm, torch, family, b, n, k), status=dmm.status())), flush=True)
+        return
+    w = torch.randint(-32768, 32768, (n, k // 8), dtype=torch.int16, device="cuda")
+    if family == "fp16":
+        cb = dmm.synthetic_codebook(42, "cuda")
+        x = torch.randn(b, k, device="cuda", dtype=torch.float16)
+        out = torch.zeros(b, n, device="cuda", dtype=torch.float32)
+        for _ in range(args.calls):
+            y = dmm.decode_matmul_fp16(x, w, cb, 1.0, out, path=args.path, accumulate=True, atomic=args.path in (0, 2, 3))
+    else:
+        cb = dmm.build_codebook_abs("cuda")
+        x = torch.randint(-128, 128, (b, k), dtype=torch.int8, device="cuda")
+        for _ in range(args.calls):
+            y = dmm.decode_matmul_i8(x, w, cb)
+    torch.cuda.synchronize()
+    print("status", dmm.status(), "checksum", float(y.float().abs().sum()))
+
+
 def main():
     args = parse()
+    if args.shape:
+        return run_shape(args)
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -189,9 +189,6 @@ static int run_stream(int family, const void *x, const void *codes, const void *
     return 0;
 }
 
-#ifdef DMM_TRACE
-static long long *g_trace = nullptr;  // device buffer for clock stamps (debug builds only)
-#endif
 
 // tcgen05 path: one launch per chunk of 64 batch columns (32 for the fp6/fp8 operand policy,
 // preceded by planes_kernel when the chunk has at least kPlanesMinBatch rows).
@@ -279,9 +276,6 @@ static int run_umma(bool f8, const void *x, int x_kind, long long x_ld, long lon
             p.next_K = t_next_hint.K;
             t_next_hint = NextHint();
         }
-#ifdef DMM_TRACE
-        p.trace = g_trace;
-#endif
         // 17 to 32 batch rows (128 MMA columns) run on the kernel of dmm_tc.cuh, measured faster there;
         // everything else on the kernel of dmm_umma.cuh
         rc = (f8 && p.M > 16 && !fast_layout) ? launch_tc_wide(p, d->num_sms, pdl, stream) : launch_umma(f8, p, d->num_sms, pdl, stream);
@@ -324,9 +318,6 @@ static int run_umma_i8(const void *x, const void *codes, const void *cb64, int32
         p.atomic_reduce = 1;
         p.sign_convention = sign_convention;
         p.fast_layout = fast_layout ? 1 : 0;
-#ifdef DMM_TRACE
-        p.trace = g_trace;
-#endif
         rc = launch_umma_i8(p, d->num_sms, (flags & DMM_FLAG_PDL) != 0, stream);
         g_launches.fetch_add(1, std::memory_order_relaxed);
         if (rc) return rc;
@@ -680,9 +671,6 @@ int dmm_f16_chain(const dmm_chain_op *ops, int n_ops, const void *cb16, int64_t 
         p[i].sign_convention = sign_convention;
         p[i].zero_ptr = o.zero_ptr;
         p[i].zero_count = o.zero_count;
-#ifdef DMM_TRACE
-        p[i].trace = g_trace;
-#endif
     }
     rc = launch_umma_chain(p, n_ops, d->chain_sync, d->num_sms, (flags & DMM_FLAG_PDL) != 0,
                            static_cast<cudaStream_t>(stream));
@@ -826,8 +814,5 @@ const char *dmm_error_string(int code) {
 
 const char *dmm_version(void) { return "0.1"; }
 
-#ifdef DMM_TRACE
-void dmm_debug_set_trace(long long *device_buffer) { g_trace = device_buffer; }
-#endif
 
 }  // extern "C"

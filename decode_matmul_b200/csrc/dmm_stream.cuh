@@ -32,13 +32,6 @@
 
 namespace dmm {
 
-struct FamI8 {
-    using x_t = int8_t;
-    using acc_t = int;
-    static constexpr int kIsF16 = 0;
-    static constexpr int kFmt = kFmtTwos;
-    static constexpr int kXRegs = 2;  // 8 int8 per k-tile per lane
-};
 struct FamF16 {
     using x_t = __half;
     using acc_t = float;
@@ -79,14 +72,9 @@ __device__ __forceinline__ void store_out(const StreamParams &p, long long ss, i
     const long long n = (ss * S + s) * 16 + (l >> 2) + 8 * (c >> 1);
     const long long col = mb * 8 + 2 * (l & 3) + (c & 1);
     if (col >= p.M || n >= p.N) return;
-    if constexpr (Fam::kIsF16) {
-        float *out = reinterpret_cast<float *>(p.out) + col * p.N + n;
-        const float r = p.scale * v;
-        *out = p.accumulate ? *out + r : r;
-    } else {
-        int *out = reinterpret_cast<int *>(p.out) + col * p.N + n;
-        *out = p.accumulate ? *out + v : v;
-    }
+    float *out = reinterpret_cast<float *>(p.out) + col * p.N + n;
+    const float r = p.scale * v;
+    *out = p.accumulate ? *out + r : r;
 }
 
 // Position of a warp in its tile sequence: the segment (super-strip) it is in and its
@@ -255,19 +243,13 @@ __global__ void __launch_bounds__(kStreamWarps * 32, 1) stream_kernel(const Stre
                             const uint32_t word = lds32(stage + s * (C * 128u) + jt * 128u);
                             const uint2 d0 = decode8<0>(word, ll);  // strip row g
                             const uint2 d1 = decode8<1>(word, ll);  // strip row g + 8
-                            if constexpr (Fam::kIsF16) {
-                                uint32_t a[4], b[4];
-                                bytes_to_half2(d0, a);
-                                bytes_to_half2(d1, b);
+                            uint32_t a[4], b[4];
+                            bytes_to_half2(d0, a);
+                            bytes_to_half2(d1, b);
 #pragma unroll
-                                for (int mb = 0; mb < MB; ++mb) {
-                                    mma_f16(acc[s][mb], a[0], b[0], a[1], b[1], xf[mb][jt][0], xf[mb][jt][1]);
-                                    mma_f16(acc[s][mb], a[2], b[2], a[3], b[3], xf[mb][jt][2], xf[mb][jt][3]);
-                                }
-                            } else {
-#pragma unroll
-                                for (int mb = 0; mb < MB; ++mb)
-                                    mma_s8(acc[s][mb], d0.x, d1.x, d0.y, d1.y, xf[mb][jt][0], xf[mb][jt][1]);
+                            for (int mb = 0; mb < MB; ++mb) {
+                                mma_f16(acc[s][mb], a[0], b[0], a[1], b[1], xf[mb][jt][0], xf[mb][jt][1]);
+                                mma_f16(acc[s][mb], a[2], b[2], a[3], b[3], xf[mb][jt][2], xf[mb][jt][3]);
                             }
                         }
                     }
@@ -366,9 +348,7 @@ inline int launch_one(const StreamParams &p_in, int num_sms, bool pdl, cudaStrea
 }
 
 inline int launch_stream(int family, const StreamParams &p, int num_sms, bool pdl, cudaStream_t stream) {
-    // The integer family runs on the tcgen05 kernel (umma_kernel<PolI8, *>); this kernel keeps its
-    // integer policy (FamI8) only as the description of that arithmetic and is no longer launched with it.
-    if (family == 0) return DMM_ERR_UNSUPPORTED;
+    if (family == 0) return DMM_ERR_UNSUPPORTED;  // the integer family runs on the tcgen05 kernel only
     if (p.M <= 8) return launch_one<FamF16, 4, 1>(p, num_sms, pdl, stream);
     return launch_one<FamF16, 2, 2>(p, num_sms, pdl, stream);
 }

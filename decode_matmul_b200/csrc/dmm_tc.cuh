@@ -28,9 +28,9 @@
 //           the two MMA tiles of a chunk are issued by two warps (so that each accumulator still
 //           has exactly one issuer and the summation order is fixed).
 //   20..23  activation loaders.  The activations of the CTA's k-tile sequence are staged round by
-//           round: a round is NACC consecutive chunks (one per issuer), kept in one of NE = 3 round
-//           buffers; loader w < NE owns buffer w and fills the rounds w mod NE.  Slot (chunk j of the round, k-tile i)
-//           sits at a fixed offset, so an issuer finds its operands without any search: it uses
+//           round: a round is NACC consecutive chunks (one per issuer), kept in one of NE round buffers
+//           (3 at the largest round size, up to 8 for small batches); loader w owns the buffers b with
+//           b mod 4 = w and fills their rounds.  Slot (chunk j of the round, k-tile i) sits at a fixed offset, so an issuer finds its operands without any search: it uses
 //           exactly one chunk of every round, in order.  The loaders are the only warps that wait
 //           for the previous kernel of the stream (programmatic dependent launch).
 //   24..27  TMA producers, one thread per decoder group: they stream that group's code chunks
@@ -104,37 +104,6 @@ __host__ __device__ inline int tc_rounds(int M) {
     const int fit = static_cast<int>((kTcRounds * kTcRoundBytes) / tc_round_bytes<Pol, NMMA>(M));
     return fit < kTcMaxRounds ? fit : kTcMaxRounds;
 }
-
-#ifdef DMM_SELFCHECK
-// Debugging aid (builds with -DDMM_SELFCHECK only): progress counters and the first bounds violation of
-// every CTA, written to a host-mapped buffer so that they survive a fault.  64 words per CTA.
-#define DMM_DBG(slot, val)                                                                            \
-    do {                                                                                              \
-        if (p.trace != nullptr) reinterpret_cast<volatile long long *>(p.trace)[blockIdx.x * 64 + (slot)] = (val); \
-    } while (0)
-#define DMM_VIOL(code, a, b2, c2)                                                                     \
-    do {                                                                                              \
-        if (p.trace != nullptr) {                                                                     \
-            volatile long long *t_ = reinterpret_cast<volatile long long *>(p.trace) + blockIdx.x * 64;  \
-            t_[32] = (code); t_[33] = (a); t_[34] = (b2); t_[35] = (c2);                              \
-        }                                                                                             \
-    } while (0)
-#else
-#define DMM_DBG(slot, val) do { } while (0)
-#define DMM_VIOL(code, a, b2, c2) do { } while (0)
-#endif
-
-#ifdef DMM_TSTAMP
-// Timeline of CTA 0 (builds with -DDMM_TSTAMP only; batch 1): clock stamps into an unused part of the
-// activation area, copied to p.trace at the end.  role 0..3, up to 64 events with 4 stamps each.
-#define DMM_TS(role, idx, what)                                                                       \
-    do {                                                                                              \
-        if (blockIdx.x == 0 && (idx) < 64)                                                            \
-            reinterpret_cast<volatile long long *>(smem_raw + kTcBarBytes + 40960)[((role) * 64 + (idx)) * 4 + (what)] = clock64(); \
-    } while (0)
-#else
-#define DMM_TS(role, idx, what) do { } while (0)
-#endif
 
 struct TcArgs {
     UmmaParams p;
@@ -243,27 +212,18 @@ __global__ void __launch_bounds__(kTcThreads, 1) dmm_kernel(const __grid_constan
         int buf = 0;             // group buffer of the next step
         uint32_t fpar = 1;       // parity to wait for on its Free barrier (the first NA steps find it free)
         int segidx = 0, ebase = 0;  // segments and chunks of this CTA so far
-        [[maybe_unused]] int ts_step = 0;
-        [[maybe_unused]] const bool ts_me = warp == 0 && lane == 0;
         for (int ss = ss_first; ss <= ss_last; ebase += seg_chunks(ss), ++ss, ++segidx) {
             const int len = seg_len(ss);
             const int nchunks_ss = (len + C - 1) / C;
             for (int c = (q - ebase) & 3; c < nchunks_ss; c += 4) {
                 const int n = len - c * C < C ? len - c * C : C;  // k-tiles in this chunk
-                if (ts_me) DMM_TS(0, ts_step, 0);
                 mbar_wait(bar(Plan::kBarCode + q * RING + slot), cpar, flags);
                 const uint32_t src = gring + slot * Plan::kSlotBytes + lane_off;
-#ifdef DMM_SELFCHECK
-                if (src < ring_addr || src + 3 * 128 + 16 > ring_addr + Plan::kRingBytes) { DMM_VIOL(1, src, ring_addr, slot); continue; }
-                if (wq == 0 && lane == 0) DMM_DBG(q, (static_cast<long long>(ss) << 32) | static_cast<unsigned>(c));
-#endif
 #pragma unroll 1
                 for (int g0 = 0; g0 < n; g0 += G) {
                     const int sl = q * NA + buf;
-                    if (ts_me && g0 > 0) DMM_TS(0, ts_step, 0);
                     mbar_wait(bar(Plan::kBarFree + sl), fpar, flags);
                     tc_fence_after();
-                    if (ts_me) DMM_TS(0, ts_step, 1);
                     const uint32_t acol = abase + static_cast<uint32_t>(buf) * Plan::kBufCols;
                     // group buffer columns: [tile][k-tile][8]; two k-tiles -> one x16 store per tile
                     uint32_t r0[8 * G], r1[8 * G];
@@ -289,16 +249,10 @@ __global__ void __launch_bounds__(kTcThreads, 1) dmm_kernel(const __grid_constan
                     static_assert(G == 2, "two k-tiles per step: one x16 store per MMA tile");
                     tmem_st16(acol, reinterpret_cast<const uint32_t(&)[16]>(r0));
                     tmem_st16(acol + G * 8, reinterpret_cast<const uint32_t(&)[16]>(r1));
-                    if (ts_me) DMM_TS(0, ts_step, 2);
                     tmem_wait_st();
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(bar(Plan::kBarFull + sl));
-                    if (ts_me) DMM_TS(0, ts_step, 3);
-                    ++ts_step;
-#ifdef DMM_SELFCHECK
-                    if (wq == 0 && lane == 0) DMM_DBG(20 + q, (static_cast<long long>(ss) << 32) | static_cast<unsigned>(c * 16 + g0));
-#endif
                     if (++buf == NA) {
                         buf = 0;
                         fpar ^= 1u;
@@ -361,9 +315,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) dmm_kernel(const __grid_constan
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar(Plan::kBarDFree));
-#ifdef DMM_SELFCHECK
-                if (wq == 0 && lane == 0) DMM_DBG(16 + q, segidx + 1);
-#endif
 
                 const int ss_a = ss * KT;
                 const bool full = len == KT;
@@ -482,7 +433,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) dmm_kernel(const __grid_constan
             uint32_t sbuf = 0, spar = 0;  // bit q: buffer index (NA == 2) and parity of group q
             static_assert(NA == 2, "buffer index kept as one bit per group");
             int segidx = 0, cbase = 0;
-            [[maybe_unused]] int ts_istep = 0;
             for (int ss = ss_first; ss <= ss_last; cbase += seg_chunks(ss), ++ss, ++segidx) {
                 const int len = seg_len(ss);
                 const int nchunks = (len + C - 1) / C;
@@ -494,31 +444,16 @@ __global__ void __launch_bounds__(kTcThreads, 1) dmm_kernel(const __grid_constan
                 for (int c = (me - cbase) & (NACC - 1); c < nchunks; c += NACC) {
                     const int q = (cbase + c) & 3;
                     const int n = len - c * C < C ? len - c * C : C;
-                    if (wi == 0 && leader) DMM_TS(1, ts_istep, 0);
                     mbar_wait(bar(Plan::kBarXReady + rb), xpar, flags);
 #pragma unroll 1
                     for (int g0 = 0; g0 < n; g0 += G) {
                         const uint32_t b = (sbuf >> q) & 1u;
                         const int sl = q * NA + static_cast<int>(b);
-                        if (wi == 0 && leader && g0 > 0) DMM_TS(1, ts_istep, 0);
-                        if (wi == 0 && leader) DMM_TS(1, ts_istep, 1);
                         mbar_wait(bar(Plan::kBarFull + sl), (spar >> q) & 1u, flags);
                         tc_fence_after();
-                        if (wi == 0 && leader) DMM_TS(1, ts_istep, 2);
                         if (leader) {
                             const uint32_t a_col = tmem + Plan::kDCols + static_cast<uint32_t>(sl) * Plan::kBufCols + a_tile;
                             const uint32_t xlo = x_cur + static_cast<uint32_t>(g0) * tile16;
-#ifdef DMM_SELFCHECK
-                            {
-                                const uint32_t xa = (xlo & 0x3FFFu) << 4;
-                                if (xa < x_addr || xa + 2 * tile_b > x_addr + kTcRounds * kTcRoundBytes + 256 || sl < 0 || sl >= Plan::kSlots) {
-                                    DMM_VIOL(3, xa, x_addr, rb);
-                                    tc_commit(bar(Plan::kBarFree + sl));
-                                    continue;
-                                }
-                                DMM_DBG(4 + wi, (static_cast<long long>(ss) << 32) | static_cast<unsigned>(c * 16 + g0));
-                            }
-#endif
 #pragma unroll
                             for (int i = 0; i < G; ++i) {
                                 if (g0 + i < n) {
@@ -533,8 +468,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) dmm_kernel(const __grid_constan
                             }
                             tc_commit(bar(Plan::kBarFree + sl));
                         }
-                        if (wi == 0 && leader) DMM_TS(1, ts_istep, 3);
-                        ++ts_istep;
                         acc = 1u;
                         sbuf ^= 1u << q;
                         if (b == 1u) spar ^= 1u << q;
@@ -568,10 +501,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) dmm_kernel(const __grid_constan
                 for (int c = (q - cbase) & 3; c < nchunks; c += 4) {
                     if (n_q >= RING) mbar_wait(bar(Plan::kBarEmpty + q * RING + slot), par, flags);
                     const uint32_t b = bar(Plan::kBarCode + q * RING + slot);
-#ifdef DMM_SELFCHECK
-                    if ((kt0 + c * C) * 32 >= p.K || (kt0 + c * C) < 0 || ss * 16 >= p.N / 16 || ss < 0) { DMM_VIOL(4, kt0 + c * C, ss, c); }
-                    DMM_DBG(12 + q, (static_cast<long long>(ss) << 32) | static_cast<unsigned>(c));
-#endif
                     mbar_arrive_expect_tx(b, Plan::kSlotBytes);
                     tma_load_2d(ring_addr + (q * RING + slot) * Plan::kSlotBytes, &args.map, (kt0 + c * C) * 32, ss * 16, b, policy);
                     ++n_q;
@@ -638,13 +567,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) dmm_kernel(const __grid_constan
                 const bool round_done = j == RCH - 1 || (ss == ss_last && c == nchunks - 1);
                 if (j == 0 && r >= NE)  // first chunk of a round: its buffer must have been given back
                     mbar_wait(bar(Plan::kBarXFree + rb), static_cast<uint32_t>(((r / NE) - 1) & 1), flags);
-#ifdef DMM_SELFCHECK
-                if (rbuf + (j * C + n) * tile_b > x_addr + kTcRounds * kTcRoundBytes || kt < 0 || (kt + n) * 32 > p.K) {
-                    DMM_VIOL(2, rbuf, kt, n);
-                    continue;
-                }
-                if (lane == 0) DMM_DBG(8 + wl, (static_cast<long long>(ss) << 32) | static_cast<unsigned>(c));
-#endif
                 if (bulk) {
                     // the planes were split once by planes_kernel: a chunk is one contiguous run
                     if (lane == 0) {
@@ -724,11 +646,6 @@ __global__ void __launch_bounds__(kTcThreads, 1) dmm_kernel(const __grid_constan
 
     tc_fence_before();
     __syncthreads();
-#ifdef DMM_TSTAMP
-    if (blockIdx.x == 0 && p.trace != nullptr)
-        for (int i = tid; i < 4 * 64 * 4; i += kTcThreads)
-            p.trace[i] = reinterpret_cast<volatile long long *>(smem_raw + kTcBarBytes + 40960)[i];
-#endif
     if (warp == kTcMmaWarp) tmem_dealloc(tmem, 512);
 }
 

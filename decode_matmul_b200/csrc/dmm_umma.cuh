@@ -351,7 +351,6 @@ struct UmmaParams {
     long long next_N, next_K;
     Part32 next_part;
     int next_grid;
-    long long *trace;    // debugging aid (builds with -DDMM_TRACE only): clock stamps of CTA 0
 };
 
 // Accumulator element of the epilogue: fp32, or int32 for the integer family.
@@ -374,15 +373,6 @@ struct UmmaChainT {
     int n_ops;
     unsigned *sync;  // [n_ops] arrival counters in global memory, zero between launches (chains only)
 };
-
-#ifdef DMM_TRACE
-#define DMM_STAMP(role, idx, what)                                                              \
-    do {                                                                                        \
-        if (ch.op[0].trace != nullptr && blockIdx.x == 0 && (idx) < 64) ch.op[0].trace[((role)*64 + (idx)) * 4 + (what)] = clock64(); \
-    } while (0)
-#else
-#define DMM_STAMP(role, idx, what) do { } while (0)
-#endif
 
 // Residual stream plus the partial products that every rank of a tensor-parallel group has pushed into
 // this rank's slots (consumer side of the slots form): eight consecutive values of one row, summed in
@@ -681,7 +671,6 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
     // the warp index through a shuffle: the compiler then knows it is the same in every lane and
     // keeps what derives from it (roles, descriptors, TMEM addresses) in uniform registers
     const int tid = threadIdx.x, warp = __shfl_sync(0xffffffffu, tid >> 5, 0), lane = tid & 31;
-    if (tid == 0) DMM_STAMP(0, 0, 0);
     const UmmaParams &p0 = ch.op[0];  // codebook, sign convention, batch and input kind are common to all ops
     const int n_ops = kChain ? ch.n_ops : 1;
     // the codebook is static data: fetch it first (fp16 table; the integer family's int64 table is read in lut_fill)
@@ -714,7 +703,6 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
     // chunk number mod 4 is the decoder group and mod kNAcc the issuer, so consecutive chunks
     // always go to different groups, also across a segment or op boundary.
 
-    if (tid == 0) DMM_STAMP(0, 2, 0);
     // ---- set-up ----
     // The decoder warps build the look-up table straight away; the other warps initialise the
     // barriers, allocate TMEM and zero the fp16 activation stages meanwhile and then go on
@@ -724,16 +712,12 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
     constexpr int n_threads = kSplit ? kUThreads : kUThreads - (kUTmaWarps - 1) * 32, n_other = n_threads - kUDecWarps * 32;
     bool bad_cb = false;
     if (warp < kUDecWarps) {
-        if (tid == 0) DMM_STAMP(0, 1, 0);
         bad_cb = lut_fill(lut_addr, p0.cb, Pol::kIsInt ? 0 : 1, p0.sign_convention, Pol::kFmt, tid, kUDecWarps * 32,
                           Pol::kIsF8 != 0 && !Pol::kIsInt, Pol::kIsInt ? nullptr : &cb_pre);
-        if (tid == 0) DMM_STAMP(0, 1, 1);
-        if (lane == 0) DMM_STAMP(0, 8 + warp, 0);
         named_barrier(4, n_threads);
     } else {
         const int ot = tid - kUDecWarps * 32;  // 0 .. n_other-1
         const int bt = ot - kUMmaWarps * 32;   // loader and TMA warps initialise the barriers
-        if (bt == 0) DMM_STAMP(0, 3, 0);
         if (bt >= 0 && bt < Plan::kBarCount) {
             uint32_t count = 1;                                                // TMA, tcgen05.commit
             if (bt >= Plan::kBarEmpty && bt < Plan::kBarFull) count = 4;
@@ -758,17 +742,12 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
         }
         fence_async_smem();
         tc_fence_before();
-        if (ot == 0) DMM_STAMP(0, 2, 2);
-        if (bt == 0) DMM_STAMP(0, 3, 1);
         named_barrier(3, n_other);
-        if (bt == 0) DMM_STAMP(0, 3, 2);
         named_barrier_arrive(4, n_threads);
-        if (bt == 0) DMM_STAMP(0, 2, 1);
     }
     tc_fence_after();
     const uint32_t tmem = __shfl_sync(0xffffffffu, *tmem_slot, 0);
     grid_dep_launch();
-    if (tid == 0) DMM_STAMP(0, 0, 1);
 
     if (warp < kUDecWarps) {
         // =============================== decoders ===============================
@@ -780,7 +759,6 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
         if (bad_cb) raise_status(DMM_STATUS_BAD_CODEBOOK);
         LutLane ll = lut_lane(lut_addr, lane, Pol::kIsF8 != 0 && !Pol::kIsInt);
         ll.two = static_cast<uint32_t>(flags[2]);
-        if (tid == 0) DMM_STAMP(0, 0, 2);
 
         const uint32_t tlane = tmem + (static_cast<uint32_t>(wq * 32) << 16);
         // Tensor-parallel producer: this launch is epoch e = counter + 1 (every CTA reads the counter before
@@ -807,9 +785,7 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
             for (int c = (q - ebase) & 3; c < nchunks_ss; c += 4) {
                 const int n = len - c * C < C ? len - c * C : C;  // k-tiles in this chunk
                 const int slot = cidx % RING;
-                if (tid == 0) DMM_STAMP(5, cidx, 0);
                 mbar_wait(bar(Plan::kBarCode + q * RING + slot), static_cast<uint32_t>((cidx / RING) & 1), flags);
-                if (tid == 0) DMM_STAMP(5, cidx, 1);
                 // slot layout [16 strips][C k-tiles][128 B]; this lane: strip 4*wq + lane/8, piece lane%8
                 const uint32_t src = gring + slot * Plan::kSlotBytes + (wq * 4 + (lane >> 3)) * (C * 128) + (lane & 7) * 16;
                 const uint32_t fsrc = gring + slot * Plan::kSlotBytes;  // (fast layout: see fetch_fast_ktile)
@@ -818,10 +794,8 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
                 for (int g0 = 0; g0 < n; g0 += G) {
                     const int buf = static_cast<int>(sA % NA);
                     const int sl = q * NA + buf;
-                    if (tid == 0) DMM_STAMP(1, sA, 0);
                     if (sA >= NA) mbar_wait(bar(Plan::kBarFree + sl), ((sA / NA) - 1) & 1, flags);
                     tc_fence_after();
-                    if (tid == 0) DMM_STAMP(1, sA, 1);
                     const uint32_t acol = tlane + Plan::kDCols + static_cast<uint32_t>(sl) * Plan::kBufCols;
                     if constexpr (Pol::kIsF8) {
                         // group buffer columns: [tile][k-tile][8]; two k-tiles -> one x16 store per tile
@@ -866,17 +840,14 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
                         tmem_st16(acol, r0);
                         tmem_st16(acol + G * Pol::kACols, r1);
                     }
-                    if (tid == 0) DMM_STAMP(1, sA, 2);
                     tmem_wait_st();
                     tc_fence_before();
                     __syncwarp();
                     if (lane == 0) mbar_arrive(bar(Plan::kBarFull + sl));
-                    if (tid == 0) DMM_STAMP(1, sA, 3);
                     ++sA;
                 }
                 __syncwarp();  // every lane has read the slot: hand it back to the TMA warp
                 if (lane == 0) mbar_arrive(bar(Plan::kBarEmpty + q * RING + slot));
-                if (tid == 0) DMM_STAMP(5, cidx, 2);
                 ++cidx;
             }
 
@@ -886,10 +857,8 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
                 // accumulator a was written in this segment iff one of its chunks has parity a
                 uint32_t used = 0;
                 for (int cc = 0; cc < nchunks && cc < NACC; ++cc) used |= 1u << ((ebase + cc) % NACC);
-                if (tid == 0) DMM_STAMP(4, segidx, 0);
                 mbar_wait(bar(Plan::kBarDReady), static_cast<uint32_t>(segidx & 1), flags);
                 tc_fence_after();
-                if (tid == 0) DMM_STAMP(4, segidx, 1);
                 // the accumulators are fp32, or int32 for the integer family (exact, no scale)
                 using Acc = typename AccType<Pol::kIsInt != 0>::type;
                 Acc v[NB];
@@ -930,7 +899,6 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
                         }
                     }
                 }
-                if (tid == 0) DMM_STAMP(4, segidx, 3);
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar(Plan::kBarDFree));
@@ -1016,7 +984,6 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
                     }
                     named_barrier(2, 256);  // flags[1] is reused by the next segment
                 }
-                if (tid == 0) DMM_STAMP(4, segidx, 2);
             }
         }
         if (kTp && p.tp_mode == 2 && q < 2) {
@@ -1126,12 +1093,10 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
 #pragma unroll 1
                     for (int g0 = 0; g0 < n; g0 += G, ++cn) {
                         const int sl = q * NA + static_cast<int>(cn % NA);
-                        if (wi == 0 && leader) DMM_STAMP(2, cn * 2 + (q >> 1), 0);
                         const uint32_t a_col = tmem + Plan::kDCols + static_cast<uint32_t>(sl) * Plan::kBufCols;
                         if constexpr (Pol::kIsF8) {
                             mbar_wait(bar(Plan::kBarFull + sl), (cn / NA) & 1, flags);
                             tc_fence_after();
-                            if (wi == 0 && leader) DMM_STAMP(2, cn * 2 + (q >> 1), 1);
                             // tile by tile (both MMA tiles of a k-tile back to back), so that an
                             // epoch is only left when nothing issued later still reads its buffer
 #pragma unroll
@@ -1173,7 +1138,6 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
                         } else {
                             mbar_wait(bar(Plan::kBarFull + sl), (cn / NA) & 1, flags);
                             tc_fence_after();
-                            if (wi == 0 && leader) DMM_STAMP(2, cn * 2 + (q >> 1), 1);
                             const uint64_t xd = xdesc0 + ((static_cast<uint32_t>(sl) * Plan::kXStage) >> 4);
                             for (int t = t_lo; t < t_hi; ++t) {
                                 const uint32_t d_col = tmem + static_cast<uint32_t>((t * NACC + me) * NMMA);
@@ -1185,7 +1149,6 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
                         }
                         first = false;
                         if (leader) tc_commit(bar(Plan::kBarFree + sl));
-                        if (wi == 0 && leader) DMM_STAMP(2, cn * 2 + (q >> 1), 2);
                     }
                     if (q == 0) cnt0 = cn; else if (q == 1) cnt1 = cn; else if (q == 2) cnt2 = cn; else cnt3 = cn;
                 }
@@ -1411,7 +1374,6 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
             // (team by the epoch number over all ops, so that the teams keep alternating across ops)
             for (int e = ((wl % kULoadTeams) - eg_base) & (kULoadTeams - 1); p.x_planes == nullptr && e < nep; e += kULoadTeams) {
                 const int eg = eg_base + e;
-                if (wl == 0 && lane == 0) DMM_STAMP(3, e, 0);
                 if (eg >= Plan::kEpochs)
                     mbar_wait(bar(Plan::kBarXFree + eg % Plan::kEpochs), static_cast<uint32_t>(((eg / Plan::kEpochs) - 1) & 1), flags);
                 const int t_lo = e == 0 ? 0 : E0 + (e - 1) * E;
@@ -1477,7 +1439,6 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
                 fence_async_smem();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar(Plan::kBarXReady + eg % Plan::kEpochs));
-                if (wl == 0 && lane == 0) DMM_STAMP(3, e, 1);
             }
             eg_base += nep;
         } else {
@@ -1530,7 +1491,6 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
 
     tc_fence_before();
     __syncthreads();
-    if (tid == 0) DMM_STAMP(0, 0, 3);
     if (warp == kUMmaWarp) tmem_dealloc(tmem, kUTmemCols);
 }
 

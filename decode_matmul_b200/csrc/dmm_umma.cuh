@@ -188,6 +188,7 @@ __device__ __forceinline__ uint4 fetch_fast_ktile(uint32_t slot_addr, int c_tile
 struct PolF8 {
     static constexpr int kIsF8 = 1;
     static constexpr int kIsInt = 0;
+    static constexpr int kFast = 0;    // 1: the codes are in the layout of fast_decode_matmul_cuda (see PolF8Fast)
     static constexpr int kFmt = kFmtFp6;
     static constexpr int kG = 2;
     static constexpr int kNA = 2;
@@ -204,6 +205,7 @@ struct PolF8 {
 struct PolI8 {
     static constexpr int kIsF8 = 1;
     static constexpr int kIsInt = 1;
+    static constexpr int kFast = 0;
     static constexpr int kFmt = kFmtTwos;
     static constexpr int kG = 2;
     static constexpr int kNA = 2;
@@ -216,6 +218,7 @@ struct PolI8 {
 struct PolF16 {
     static constexpr int kIsF8 = 0;
     static constexpr int kIsInt = 0;
+    static constexpr int kFast = 0;
     static constexpr int kFmt = kFmtOffset;
     static constexpr int kG = 1;
     static constexpr int kNA = 2;
@@ -224,6 +227,14 @@ struct PolF16 {
     static constexpr int kACols = 16;  // 32 k x 2 bytes
     static constexpr uint32_t x_tile_bytes(int nmma) { return static_cast<uint32_t>(nmma) * 64u; }  // 4 k-chunks x rows x 16 B
     static constexpr int out_cols(int nmma) { return nmma; }
+};
+// The same kernels over codes in the layout of fast_decode_matmul_cuda: their own instantiations, so that the
+// tile-layout kernels carry nothing of it (a run-time switch in the decoders' inner loop cost them 9 %).
+struct PolF8Fast : PolF8 {
+    static constexpr int kFast = 1;
+};
+struct PolI8Fast : PolI8 {
+    static constexpr int kFast = 1;
 };
 
 constexpr int kUDecWarps = 16, kUMmaWarp = 16, kUMmaWarps = 4, kULoadWarps = 4, kULoadTeams = 2, kUTmaWarp = 24, kUTmaWarps = 4;
@@ -789,7 +800,7 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
                 // slot layout [16 strips][C k-tiles][128 B]; this lane: strip 4*wq + lane/8, piece lane%8
                 const uint32_t src = gring + slot * Plan::kSlotBytes + (wq * 4 + (lane >> 3)) * (C * 128) + (lane & 7) * 16;
                 const uint32_t fsrc = gring + slot * Plan::kSlotBytes;  // (fast layout: see fetch_fast_ktile)
-                const bool fast = Pol::kIsF8 && p0.fast_layout != 0;
+                constexpr bool fast = Pol::kFast != 0;
 #pragma unroll 1
                 for (int g0 = 0; g0 < n; g0 += G) {
                     const int buf = static_cast<int>(sA % NA);
@@ -907,7 +918,7 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
                 const bool full = len == KT;
                 const int my_slot = seg_kt0(ss) > 0 ? 0 : 1;
                 const int trow = wq * 32 + lane;  // TMEM lane = row of the MMA tile
-                const long long n = (Pol::kIsF8 && p.fast_layout != 0)
+                const long long n = Pol::kFast
                                         ? static_cast<long long>(ss) * 256 + 32 * (4 * q + wq) + lane
                                         : (static_cast<long long>(ss) * 16 + wq * 4 + (lane >> 3)) * 16 + 8 * q + (lane & 7);
                 const int ptid = q * 128 + trow;
@@ -1190,7 +1201,7 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
                         if (n_q >= RING) mbar_wait(bar(Plan::kBarEmpty + q * RING + slot), par, flags);
                         const uint32_t b = bar(Plan::kBarCode + q * RING + slot);
                         mbar_arrive_expect_tx(b, Plan::kSlotBytes);
-                        tma_load_2d(ring_addr + (q * RING + slot) * Plan::kSlotBytes, &ch.map[0], (kt0 + c * C) * (p.fast_layout ? 64 : 32), ss * (p.fast_layout ? 8 : 16), b, policy);
+                        tma_load_2d(ring_addr + (q * RING + slot) * Plan::kSlotBytes, &ch.map[0], (kt0 + c * C) * (Pol::kFast ? 64 : 32), ss * (Pol::kFast ? 8 : 16), b, policy);
                         ++n_q;
                         if (++slot == RING) {
                             slot = 0;
@@ -1228,7 +1239,7 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
                         mbar_wait(bar(Plan::kBarEmpty + q * RING + slot), ((n_q / RING) - 1) & 1, flags);
                     const uint32_t b = bar(Plan::kBarCode + q * RING + slot);
                     mbar_arrive_expect_tx(b, Plan::kSlotBytes);
-                    tma_load_2d(ring_addr + (q * RING + slot) * Plan::kSlotBytes, &ch.map[op], (kt0 + c * C) * (p.fast_layout ? 64 : 32), ss * (p.fast_layout ? 8 : 16), b, policy);
+                    tma_load_2d(ring_addr + (q * RING + slot) * Plan::kSlotBytes, &ch.map[op], (kt0 + c * C) * (Pol::kFast ? 64 : 32), ss * (Pol::kFast ? 8 : 16), b, policy);
                     if (q == 0) ++cnt[0]; else if (q == 1) ++cnt[1]; else if (q == 2) ++cnt[2]; else ++cnt[3];
                 }
             }
@@ -1559,10 +1570,10 @@ inline int launch_umma_ops(const UmmaParams *ops, int n_ops, unsigned *sync, int
     auto kernel = umma_kernel<Pol, NMMA, kChain, false>;
     // four TMA producer warps up to two batch rows of the fp16 family (measured 1 % faster at batch 1), else one
     bool split = false;
-    if constexpr (Pol::kIsF8 && !kChain) {  // tensor-parallel epilogue: its own instantiation, nothing of it in the plain kernel
+    if constexpr (Pol::kIsF8 && !kChain && !Pol::kFast) {  // tensor-parallel epilogue: its own instantiation, nothing of it in the plain kernel
         if (ops[0].n_peers > 0 || ops[0].move_count > 0 || ops[0].tp_mode != 0) kernel = umma_kernel<Pol, NMMA, kChain, true>;
     }
-    if constexpr (Pol::kIsF8 && !Pol::kIsInt && !kChain && NMMA == 32) {
+    if constexpr (Pol::kIsF8 && !Pol::kIsInt && !kChain && NMMA == 32 && !Pol::kFast) {
         if (ops[0].M <= 2) {
             split = true;
             kernel = umma_kernel<Pol, NMMA, kChain, false, true>;
@@ -1600,8 +1611,9 @@ inline int launch_umma_ops(const UmmaParams *ops, int n_ops, unsigned *sync, int
                 p.next_part.b = static_cast<int>(Tn % gn);
             }
         }
-        if (p.fast_layout) p.next_codes = nullptr;  // (the prefetch hint describes the tile layout)
-        const int rc = make_codes_map(&ch.map[i], p.codes, p.N, p.K, Pol::kC, Pol::kIsF8 && p.fast_layout != 0);
+        if (Pol::kFast) p.next_codes = nullptr;  // (the prefetch hint describes the tile layout)
+        if ((p.fast_layout != 0) != (Pol::kFast != 0)) return DMM_ERR_ARG;
+        const int rc = make_codes_map(&ch.map[i], p.codes, p.N, p.K, Pol::kC, Pol::kFast != 0);
         if (rc) return rc;
     }
     cudaLaunchConfig_t cfg = {};
@@ -1661,12 +1673,21 @@ inline int launch_planes(const void *x, int x_mode, long long x_ld, long long x_
 
 // Integer family: int8 activations, up to 32 batch rows per launch, int32 result.
 inline int launch_umma_i8(const UmmaParams &p, int num_sms, bool pdl, cudaStream_t stream) {
+    if (p.fast_layout) {
+        if (p.M <= 16) return launch_umma_one<PolI8Fast, 16>(p, num_sms, pdl, stream);
+        return launch_umma_one<PolI8Fast, 32>(p, num_sms, pdl, stream);
+    }
     if (p.M <= 16) return launch_umma_one<PolI8, 16>(p, num_sms, pdl, stream);
     return launch_umma_one<PolI8, 32>(p, num_sms, pdl, stream);
 }
 
 // f8 != 0: PolF8 (needs M <= 32); else PolF16 with M <= 64.
 inline int launch_umma(bool f8, const UmmaParams &p, int num_sms, bool pdl, cudaStream_t stream) {
+    if (f8 && p.fast_layout) {
+        if (p.M <= 8) return launch_umma_one<PolF8Fast, 32>(p, num_sms, pdl, stream);
+        if (p.M <= 16) return launch_umma_one<PolF8Fast, 64>(p, num_sms, pdl, stream);
+        return launch_umma_one<PolF8Fast, 128>(p, num_sms, pdl, stream);
+    }
     if (f8) {
         if (p.M <= 8) return launch_umma_one<PolF8, 32>(p, num_sms, pdl, stream);
         if (p.M <= 16) return launch_umma_one<PolF8, 64>(p, num_sms, pdl, stream);

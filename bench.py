@@ -456,7 +456,7 @@ def run_ours(args):
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "f16 x 2-bit codes (fp6/fp8 tensor-core operands, fp32 accumulate)", "data": "synthetic",
-            "config": workload_config(args, world),
+            "config": dict(workload_config(args, world), **({"tp_form": getattr(stack, "tp_form_used", "nccl")} if world > 1 else {})),
             "e2e": {"value": e2e, "unit": UNIT, "ms_per_step": ms_e2e, "h2d_bytes_per_step": B * H * 4,
                     "d2h_bytes_per_step": B * H * 4},
             "gpu_launches": int(launches_per_step) * args.steps,

@@ -744,6 +744,18 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
                 flags[0] = 0;
                 flags[1] = 0;
                 flags[2] = 2;
+                if constexpr (kTp) {
+                    // Slots form: word 18 of a rank's flag array is the epoch in production.  CTA 0 of a producer
+                    // sets it before any of its threads lets dependent kernels start; a consumer reads it before
+                    // it lets the next producer start, and so never needs to wait for the producer kernel as a
+                    // whole -- the producer's flags tell it when the data it reads is complete.
+                    if (p0.tp_mode == 2 && cta == 0) {
+                        unsigned *w = p0.tp_flags[p0.tp_rank];
+                        *reinterpret_cast<volatile unsigned *>(w + 18) = *reinterpret_cast<volatile const unsigned *>(w + 16) + 1u;
+                        __threadfence();
+                    }
+                    if (p0.tp_mode == 3) flags[3] = static_cast<int>(*reinterpret_cast<volatile const unsigned *>(p0.tp_flags[p0.tp_rank] + 18));
+                }
             }
             fence_mbar_init();
         }
@@ -758,7 +770,9 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
     }
     tc_fence_after();
     const uint32_t tmem = __shfl_sync(0xffffffffu, *tmem_slot, 0);
-    grid_dep_launch();
+    // (a consumer of the slots form lets the next kernel start only once its loaders have seen the producer's
+    // flags: the kernels after it then find that producer's epoch counter moved on)
+    if (!(kTp && p0.tp_mode == 3)) grid_dep_launch();
 
     if (warp < kUDecWarps) {
         // =============================== decoders ===============================
@@ -772,14 +786,12 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
         ll.two = static_cast<uint32_t>(flags[2]);
 
         const uint32_t tlane = tmem + (static_cast<uint32_t>(wq * 32) << 16);
-        // Tensor-parallel producer: this launch is epoch e = counter + 1 (every CTA reads the counter before
-        // the last CTA to finish moves it on) and accumulates into this rank's own slot of parity e & 1.
+        // Tensor-parallel producer: this launch is epoch e = counter + 1 and accumulates into this rank's own
+        // slot of parity e & 1.  The counter is read at the first epilogue, i.e. after this kernel's loaders
+        // have seen the kernel before it finish (so the producer before this one has moved it on), and stays
+        // put until the last CTA of this launch has seen every other CTA finish.
         [[maybe_unused]] unsigned tp_epoch = 0;
         [[maybe_unused]] float *tp_slot_mine = nullptr;
-        if (kTp && p0.tp_mode == 2) {
-            tp_epoch = *reinterpret_cast<volatile const unsigned *>(p0.tp_flags[p0.tp_rank] + 16) + 1u;
-            tp_slot_mine = p0.peer_out[p0.tp_rank] + (static_cast<long long>(tp_epoch & 1u) * p0.tp_world + p0.tp_rank) * p0.tp_count;
-        }
         // The four groups share the shared-memory look-up pipe and are otherwise independent:
         // start them a fraction of a group apart so that one group's hand-over and waiting
         // falls into the others' look-up bursts instead of all groups idling together.
@@ -876,7 +888,11 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
 #pragma unroll
                 for (int b = 0; b < NB; ++b) v[b] = Acc(0);
                 Acc *out_acc = reinterpret_cast<Acc *>(p.out);
-                if (kTp && p.tp_mode == 2) out_acc = reinterpret_cast<Acc *>(tp_slot_mine);
+                if (kTp && p.tp_mode == 2) {
+                    tp_epoch = *reinterpret_cast<volatile const unsigned *>(p.tp_flags[p.tp_rank] + 16) + 1u;
+                    tp_slot_mine = p.peer_out[p.tp_rank] + (static_cast<long long>(tp_epoch & 1u) * p.tp_world + p.tp_rank) * p.tp_count;
+                    out_acc = reinterpret_cast<Acc *>(tp_slot_mine);
+                }
                 Acc *const partials_acc = reinterpret_cast<Acc *>(p.partials);
                 if (Pol::kIsF8 && !Pol::kIsInt && p.M == 1) {
                     // batch 1: only column 8 * plane of every accumulator carries data; fetch those
@@ -1017,19 +1033,28 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
                 __threadfence();
                 const long long n4 = p.tp_count / 4;
                 const long long slot_off = (static_cast<long long>(tp_epoch & 1u) * p.tp_world + p.tp_rank) * p.tp_count;
-                for (long long i = et; i < n4; i += 256) {
-                    const float4 v = __ldcg(reinterpret_cast<const float4 *>(tp_slot_mine) + i);
-                    for (int r = 0; r < p.tp_world; ++r)
-                        if (r != p.tp_rank) reinterpret_cast<float4 *>(p.peer_out[r] + slot_off)[i] = v;
+                // (eight loads in flight per thread before the first store: the loop is one L2 round trip per
+                // 32 KB instead of one per 4 KB)
+                for (long long i0 = et; i0 < n4; i0 += 256 * 8) {
+                    float4 v[8];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u)
+                        if (i0 + u * 256 < n4) v[u] = __ldcg(reinterpret_cast<const float4 *>(tp_slot_mine) + i0 + u * 256);
+                    for (int r = 0; r < p.tp_world; ++r) {
+                        if (r == p.tp_rank) continue;
+                        float4 *dst = reinterpret_cast<float4 *>(p.peer_out[r] + slot_off);
+#pragma unroll
+                        for (int u = 0; u < 8; ++u)
+                            if (i0 + u * 256 < n4) dst[i0 + u * 256] = v[u];
+                    }
                 }
-                __threadfence_system();
+                if (et == 0) {
+                    *reinterpret_cast<volatile unsigned *>(p.tp_flags[p.tp_rank] + 16) = tp_epoch;  // the epoch counter moves on
+                }
+                // one release per flag covers the stores of all 256 threads (the barrier orders them before it)
                 named_barrier(2, 256);
                 if (et < p.tp_world)
                     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.tp_flags[et] + p.tp_rank), "r"(tp_epoch) : "memory");
-                if (et == 0) {
-                    __threadfence();
-                    *reinterpret_cast<volatile unsigned *>(p.tp_flags[p.tp_rank] + 16) = tp_epoch;  // the epoch counter moves on
-                }
             }
             named_barrier(2, 256);
         }
@@ -1260,7 +1285,8 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
     } else {
         // =========================== activation loaders ===========================
         // loader wl serves the chunks of parity wl (the chunks of issuer wl), one chunk per pass
-        grid_dep_wait();
+        // (a consumer of the slots form waits for the producer's flags instead, see below)
+        if (!(kTp && p0.tp_mode == 3)) grid_dep_wait();
         const int wl = warp - kUMmaWarp - kUMmaWarps;  // warps 20 .. 23
         uint32_t cnt0 = 0, cnt1 = 0;  // fp16 policy: groups staged so far for decoder groups wl and wl + 2
         int cbase = 0;
@@ -1275,6 +1301,33 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
                 if (lane == 0) grid_wait(ch.sync + (op - 1), gridDim.x, flags);
                 __syncwarp();
             }
+        }
+        // Tensor-parallel consumer: wait (bounded) until every rank, this one included, has pushed the partial
+        // product of the row-parallel layer before this one (epoch e, read in the prologue), then read the
+        // activations as residual + all slots of that epoch's parity.  This wait stands in for the wait on the
+        // previous kernel: this rank's own flag goes up only after every CTA of that kernel has finished, so
+        // what it read may be cleared below and what it wrote is complete, and the kernels before it had
+        // finished before it could.
+        [[maybe_unused]] const float *tp_slots_now = nullptr;
+        if (kTp && p.tp_mode == 3) {
+            const unsigned e = static_cast<unsigned>(flags[3]);
+            if (lane < p.tp_world) {
+                const unsigned *mine = p.tp_flags[p.tp_rank] + lane;
+                const long long t0 = clock64();
+                for (;;) {
+                    unsigned v;
+                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+                    if (static_cast<int>(v - e) >= 0) break;
+                    if (clock64() - t0 > p.tp_wait) {
+                        raise_status(DMM_STATUS_WAIT_TIMEOUT);
+                        break;
+                    }
+                    __nanosleep(40);
+                }
+            }
+            __syncwarp();
+            grid_dep_launch();
+            tp_slots_now = p.peer_out[p.tp_rank] + static_cast<long long>(e & 1u) * p.tp_world * p.tp_count;
         }
         if (p.zero_ptr != nullptr) {  // a later kernel or op will accumulate into it
             constexpr int ZT = kULoadWarps * 32;
@@ -1308,29 +1361,6 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
             __threadfence();
             __syncwarp();
             if (lane == 0) mbar_arrive(bar(Plan::kBarGridOk));
-        }
-        // Tensor-parallel consumer: wait (bounded) until every rank has pushed the partial product of the
-        // row-parallel layer before this one -- epoch = this rank's counter, moved on by that layer's kernel,
-        // which has finished -- then read the activations as residual + all slots of that epoch's parity.
-        [[maybe_unused]] const float *tp_slots_now = nullptr;
-        if (kTp && p.tp_mode == 3) {
-            const unsigned e = *reinterpret_cast<volatile const unsigned *>(p.tp_flags[p.tp_rank] + 16);
-            if (lane < p.tp_world) {
-                const unsigned *mine = p.tp_flags[p.tp_rank] + lane;
-                const long long t0 = clock64();
-                for (;;) {
-                    unsigned v;
-                    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
-                    if (static_cast<int>(v - e) >= 0) break;
-                    if (clock64() - t0 > p.tp_wait) {
-                        raise_status(DMM_STATUS_WAIT_TIMEOUT);
-                        break;
-                    }
-                    __nanosleep(40);
-                }
-            }
-            __syncwarp();
-            tp_slots_now = p.peer_out[p.tp_rank] + static_cast<long long>(e & 1u) * p.tp_world * p.tp_count;
         }
         [[maybe_unused]] const __half *x = reinterpret_cast<const __half *>(p.x);
         const int M = static_cast<int>(p.M);

@@ -324,12 +324,16 @@ class LinearStack:
 
             peer = self._peer_state(h.shape[0])
             if peer is not None:
-                # measured on B200, ms per step at batch 1, 2 ranks: pull 5.39, slots 5.93 (the copy to the peers by
-                # the producer's last CTA and the ticket all CTAs pass cost more than the small kernel they
-                # replace); earlier: pull 5.36 / 4.84 / 5.63 and push 5.67 / - / 5.37 at 2 / 4 / 8 ranks
-                mode = self.tp_mode or os.environ.get("DMM_TP_MODE", "pull" if self.world <= 4 else "push")
+                # The slots form (no cross-rank kernel, no barrier) is the fastest at every rank count measured on
+                # B200 at batch 1; it splits the activations inside the kernel, so larger batches take the
+                # one-shot all-reduce kernel (few ranks) or the epilogues that add into every rank (many ranks).
+                default = "slots" if h.shape[0] <= 8 else ("pull" if self.world <= 2 else "push")
+                mode = self.tp_mode or os.environ.get("DMM_TP_MODE", default)
+                if mode == "slots" and h.shape[0] > 8 and self.world > 2:
+                    mode = "push"
                 if mode == "slots" and h.shape[0] > 8:
                     mode = "pull"  # the slots form splits the activations inside the kernel: small batches only
+                self.tp_form_used = mode  # what a step of this stack ran last: "slots" | "push" | "pull"
                 if mode == "slots":
                     return self._step_fused_slots(h, peer)
                 if mode == "push":

@@ -173,6 +173,10 @@ int dmm_f16_fused_tp(const void *x, int x_kind, int64_t x_ld, int64_t x_gap, con
  * the activations as h_in + the slots of all ranks, summed in rank order (every rank gets the same bits);
  * the sum, the new residual stream, is also written to h_out ([M, K] fp32 like h_in; another buffer than
  * h_in).  Result: out (+)= scale * fp16(h_out) . W^T with atomic adds, as dmm_f16_fused with DMM_X_F32.
+ * Ordering on the stream: a consume call must directly follow the produce call whose partial products it
+ * reads (as the step of a transformer block does).  The consumer does not wait for that kernel as a whole:
+ * this rank's own flag, raised after every CTA of the producer has finished, stands in for it, and the
+ * consumer lets the kernel after it start only once it has seen the flags.
  * dmm_tp_finalize: h_out = h_in + slots of the last epoch, as a small kernel (end of a step).
  * Batch M <= 8.  flags: DMM_FLAG_PDL only.  Two slot parities suffice: a rank can start epoch e + 2 only
  * after every rank has finished reading epoch e.

@@ -653,10 +653,18 @@ template <class Pol, int NMMA>
 inline int launch_tc(const UmmaParams &params, int num_sms, bool pdl, cudaStream_t stream) {
     using Plan = TcPlan<Pol, NMMA>;
     auto kernel = dmm_kernel<Pol, NMMA, false>;
-    if (params.n_peers > 0 || params.move_count > 0) kernel = dmm_kernel<Pol, NMMA, true>;
-    cudaError_t err =
-        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Plan::kDynBytes));
+    const bool tp_variant = params.n_peers > 0 || params.move_count > 0;
+    if (tp_variant) kernel = dmm_kernel<Pol, NMMA, true>;
+    // the shared-memory attribute is set once per kernel variant and device, not on every launch
+    static std::atomic<unsigned long long> attr_done[2];
+    int dev = 0;
+    cudaError_t err = cudaGetDevice(&dev);
     if (err != cudaSuccess) return err;
+    if (dev >= 64 || !((attr_done[tp_variant ? 1 : 0].load(std::memory_order_acquire) >> dev) & 1ull)) {
+        err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Plan::kDynBytes));
+        if (err != cudaSuccess) return err;
+        if (dev < 64) attr_done[tp_variant ? 1 : 0].fetch_or(1ull << dev, std::memory_order_release);
+    }
     TcArgs args = {};
     UmmaParams &p = args.p;
     p = params;

@@ -48,6 +48,7 @@
 #pragma once
 #include <cuda.h>
 
+#include <atomic>
 #include "dmm_common.cuh"
 #include "dmm_launch.h"
 
@@ -1600,8 +1601,9 @@ inline int launch_umma_ops(const UmmaParams *ops, int n_ops, unsigned *sync, int
     auto kernel = umma_kernel<Pol, NMMA, kChain, false>;
     // four TMA producer warps up to two batch rows of the fp16 family (measured 1 % faster at batch 1), else one
     bool split = false;
+    [[maybe_unused]] const bool tp_variant = ops[0].n_peers > 0 || ops[0].move_count > 0 || ops[0].tp_mode != 0;
     if constexpr (Pol::kIsF8 && !kChain && !Pol::kFast) {  // tensor-parallel epilogue: its own instantiation, nothing of it in the plain kernel
-        if (ops[0].n_peers > 0 || ops[0].move_count > 0 || ops[0].tp_mode != 0) kernel = umma_kernel<Pol, NMMA, kChain, true>;
+        if (tp_variant) kernel = umma_kernel<Pol, NMMA, kChain, true>;
     }
     if constexpr (Pol::kIsF8 && !Pol::kIsInt && !kChain && NMMA == 32 && !Pol::kFast) {
         if (ops[0].M <= 2) {
@@ -1610,9 +1612,17 @@ inline int launch_umma_ops(const UmmaParams *ops, int n_ops, unsigned *sync, int
             if (ops[0].n_peers > 0 || ops[0].move_count > 0 || ops[0].tp_mode != 0) kernel = umma_kernel<Pol, NMMA, kChain, true, true>;
         }
     }
-    cudaError_t err =
-        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Plan::kDynBytes));
+    // the shared-memory attribute is set once per kernel variant and device, not on every launch
+    static std::atomic<unsigned long long> attr_done[4];
+    const int variant = (tp_variant ? 1 : 0) | (split ? 2 : 0);
+    int dev = 0;
+    cudaError_t err = cudaGetDevice(&dev);
     if (err != cudaSuccess) return err;
+    if (dev >= 64 || !((attr_done[variant].load(std::memory_order_acquire) >> dev) & 1ull)) {
+        err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(Plan::kDynBytes));
+        if (err != cudaSuccess) return err;
+        if (dev < 64) attr_done[variant].fetch_or(1ull << dev, std::memory_order_release);
+    }
     UmmaChainT<kChain ? kMaxOps : 1> ch = {};
     ch.n_ops = n_ops;
     ch.sync = sync;

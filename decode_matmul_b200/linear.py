@@ -151,6 +151,11 @@ class LinearStack:
             n_gu = self.layers[0]["gate_up"].out_features
             mk = lambda n: torch.zeros((batch, n), dtype=torch.float32, device=self.device)
             self._buf = {"a": mk(n_qkv), "g": mk(n_gu), "po": mk(self.hidden), "pd": mk(self.hidden)}
+            # scratch of this stack's own (two stacks on two streams must not share the library's buffer)
+            from .ops import workspace_bytes
+
+            need = max(workspace_bytes(batch, lin.out_features, lin.in_features) for lin in self.layers[0].values())
+            self._buf["ws"] = torch.zeros((need,), dtype=torch.uint8, device=self.device)
             self._buf_key = key
         return self._buf
 
@@ -220,7 +225,7 @@ class LinearStack:
         res, cur = peer["res"], peer["cur"]
         res[cur].copy_(h)  # the other buffer is zero (invariant kept by every row-parallel kernel)
         a.zero_()
-        kw = dict(accumulate=True, atomic=True, pdl=True)
+        kw = dict(accumulate=True, atomic=True, pdl=True, workspace=buf["ws"])
         for blk in self.layers:
             q, o, gu, dn = blk["qkv"], blk["o"], blk["gate_up"], blk["down"]
             mm(res[cur], q.codes, q.codebook, q.scale, a, x_kind=_lib.X_F32, zero=g, **kw)
@@ -255,7 +260,7 @@ class LinearStack:
         cur = 0
         h2[cur].copy_(h)
         a.zero_()
-        kw = dict(accumulate=True, atomic=True, pdl=True)
+        kw = dict(accumulate=True, atomic=True, pdl=True, workspace=buf["ws"])
         mm, hint = _ops.decode_matmul_fused, _ops.hint_next_weights
         for i, blk in enumerate(self.layers):
             q, o, gu, dn = blk["qkv"], blk["o"], blk["gate_up"], blk["down"]
@@ -294,7 +299,7 @@ class LinearStack:
         ffn_loc = self.ffn // self.world
         part, cur = peer["res"], peer["cur"]
         a.zero_()
-        kw = dict(accumulate=True, atomic=True, pdl=True)
+        kw = dict(accumulate=True, atomic=True, pdl=True, workspace=buf["ws"])
         from . import ops as _ops
 
         hint = lambda w: _ops.hint_next_weights(w)
@@ -372,7 +377,7 @@ class LinearStack:
         for i, blk in enumerate(self.layers):
             q, o, gu, dn = blk["qkv"], blk["o"], blk["gate_up"], blk["down"]
             nxt = self.layers[i + 1]["qkv"].codes if i + 1 < len(self.layers) else None
-            kw = dict(accumulate=True, atomic=True, pdl=True)
+            kw = dict(accumulate=True, atomic=True, pdl=True, workspace=buf["ws"])
             # before every product: which weights the product after it will stream (its kernel prefetches
             # their first codes into L2, so the next launch does not start with a DRAM round trip)
             hint(o.codes)

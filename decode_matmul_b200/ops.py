@@ -94,7 +94,8 @@ def decode_matmul_fp16(x, weights_compressed, codebook_fp16, scale=1.0, output=N
 
 
 def decode_matmul_fused(x, weights_compressed, codebook_fp16, scale, output, *, x_kind=_lib.X_F32, k=None, x_gap=0,
-                        sign_convention=_lib.SIGN_SLOW, accumulate=False, pdl=False, atomic=False, zero=None):
+                        sign_convention=_lib.SIGN_SLOW, accumulate=False, pdl=False, atomic=False, zero=None,
+                        workspace=None):
     """``decode_matmul_fp16`` reading the previous layer's fp32 output directly.
 
     ``x`` is fp32 [M, ld] (or fp16 with ``x_kind=X_F16``); the kernel's loaders round it to fp16
@@ -102,7 +103,10 @@ def decode_matmul_fused(x, weights_compressed, codebook_fp16, scale, output, *, 
     (``X_F32_SILU_MUL``), so no separate cast / activation kernel runs between two layers.
     ``k`` is the reduction length (default: the whole row); the result is written or added to
     ``output`` (fp32 [M, N]).  ``zero``: an fp32 tensor that this kernel clears on its way (the
-    output of a later ``atomic`` call); it must not be an operand of this call or the one before."""
+    output of a later ``atomic`` call); it must not be an operand of this call or the one before.
+    ``workspace``: a zero-initialised uint8 tensor of at least ``workspace_bytes(M, N, K)`` bytes that this
+    call uses as scratch instead of the library's buffer (calls that may overlap on the GPU, e.g. two stacks
+    on two streams, need distinct ones)."""
     _check_input(x, "x", torch.float16 if x_kind == _lib.X_F16 else torch.float32)
     _check_input(weights_compressed, "weights_compressed", torch.int16)
     _check_input(codebook_fp16, "codebook_fp16", torch.float16)
@@ -122,9 +126,16 @@ def decode_matmul_fused(x, weights_compressed, codebook_fp16, scale, output, *, 
         rc = _lib.lib().dmm_f16_fused(_ptr(x), x_kind, ld, x_gap, _ptr(weights_compressed), _ptr(codebook_fp16),
                                       float(scale), _ptr(output), M, N, K, sign_convention, _lib.LAYOUT_TILE,
                                       _lib.PATH_AUTO, flags, None if zero is None else _ptr(zero),
-                                      0 if zero is None else zero.numel(), None, 0, _stream_ptr(x.device))
+                                      0 if zero is None else zero.numel(), None if workspace is None else _ptr(workspace),
+                                      0 if workspace is None else workspace.numel() * workspace.element_size(),
+                                      _stream_ptr(x.device))
     _lib.check(rc, "decode_matmul_fused")
     return output
+
+
+def workspace_bytes(M: int, N: int, K: int) -> int:
+    """Bytes of scratch a call of shape (M, N, K) needs (``dmm_workspace_bytes``)."""
+    return int(_lib.lib().dmm_workspace_bytes(M, N, K))
 
 
 def decode_matmul_fused_tp(x, weights_compressed, codebook_fp16, scale, peer_out_ptrs, out_shape, *, x_kind=_lib.X_F32,

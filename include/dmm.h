@@ -18,10 +18,11 @@
  *                  output columns, as the reference's fast kernel reads them
  *                  (fast_decode_matmul_cuda.cu:106,110-113,130); that kernel's k addressing is
  *                  not self-consistent, so the k order is this library's completion of it.
- *                  Needs N % 32 == 0.  Every entry point accepts it: the codes are re-tiled into
- *                  a library-owned device buffer first (one extra pass over the codes, and a
- *                  cudaMalloc when the buffer has to grow), then the call proceeds as for the
- *                  tile layout.
+ *                  Needs N % 32 == 0.  dmm_i8, dmm_f16 and dmm_f16_fused stream it as it lies in
+ *                  memory on their default paths (own tensor map and lane-to-row mapping, no
+ *                  extra pass).  Only the cross-check paths (DMM_PATH_GEMV, DMM_PATH_TCGEN05)
+ *                  re-tile it into a library-owned device buffer first, which is never freed and
+ *                  cannot be grown while the stream is being captured.
  *   cb64           int64[256]; byte i of entry e is int8(4 * codebook value i)
  *                  (test_decode_matmul.py:85).
  *   cb16           fp16[256][8]; the same table as real values (byte / 4).

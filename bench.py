@@ -190,6 +190,9 @@ def run_reference(args):
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": info["cores"], "kind": "port", "sample": info["sample"]},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
+        "reference_gpu_kernel": {"unavailable": "decode_matmul_cuda.cu builds only as a torch extension through the "
+                                 "reference's own setup.py and accepts M = 8, K % 2048 == 0 only: it cannot run the "
+                                 "batch-1 fp16 workload of the metric; the CPU path above is the reference arm"},
     }
     print(json.dumps(line), flush=True)
 

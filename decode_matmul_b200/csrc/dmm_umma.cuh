@@ -1353,7 +1353,7 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
                  i += static_cast<long long>(gridDim.x) * ZT) {
                 const float v = __ldcg(p.move_src + i);
                 p.move_src[i] = 0.f;
-                atomicAdd(p.move_dst + i, v);  // other ranks may already be adding their products
+                atomicAdd_system(p.move_dst + i, v);  // other ranks may already be adding their products (system scope, as theirs)
             }
         }
         if (n_ops > 1) {

@@ -264,7 +264,10 @@ int dmm_f16_chain(const dmm_chain_op *ops, int n_ops, const void *cb16, int64_t 
  * Limits: M <= 8 and N <= 262144 (DMM_ERR_LIMIT beyond), tile layout only.  The array is
  * about 2.6 MB and every GPU that loads the library holds it until the process exits.
  * The first call on each device looks up the array's device address
- * (cudaGetSymbolAddress); make that first call outside any stream capture.  All calls on
+ * (cudaGetSymbolAddress); make that first call outside any stream capture.  With lazy module
+ * loading (the CUDA default) the array and the kernel are placed in device memory at that first
+ * call, so it must come before the host's own pool takes all of the device memory.
+ * flags: DMM_FLAG_ACCUMULATE and DMM_FLAG_PDL only (DMM_ERR_ARG for any other bit).  All calls on
  * a device share the one array: two calls that can overlap on the GPU (different streams)
  * race on it and must be serialised by the caller.  Results equal dmm_f16 with
  * DMM_PATH_TCGEN05_F8.

@@ -301,6 +301,10 @@ def run_ours(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
+        # NCCL serves set-up barriers and the parity check only (the timed step has no NCCL call), and this
+        # process leaves without tearing the group down (see the end of this function): keep its buffers off
+        # NVLink multicast objects, which must not be left bound when a rank exits
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=dev)
 
     cfg = dict(LLAMA2_70B, layers=args.layers)

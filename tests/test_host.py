@@ -153,3 +153,15 @@ def test_build_x_weights_shapes_and_ranges():
     torch.random.manual_seed(42)
     x2, w2 = dmm.build_x_weights(8, 64, 4096, "cpu")
     assert torch.equal(x, x2) and torch.equal(w, w2)
+
+
+def test_workspace_bytes_without_a_gpu():
+    """dmm_workspace_bytes is host arithmetic (tickets + stream-K partial sums + activation planes): callable
+    without a device, positive for valid shapes, growing with the batch, and what LinearStack sizes its own
+    scratch by."""
+    import decode_matmul_b200 as dmm
+
+    small = dmm.workspace_bytes(1, 8192, 8192)
+    big = dmm.workspace_bytes(32, 57344, 8192)
+    assert small > 0 and big >= small
+    assert dmm.workspace_bytes(1, 8, 64) == 0  # fewer than 16 rows: no such product

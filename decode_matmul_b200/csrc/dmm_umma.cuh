@@ -896,7 +896,8 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
                 }
                 Acc *const partials_acc = reinterpret_cast<Acc *>(p.partials);
                 if (Pol::kIsF8 && !Pol::kIsInt && p.M == 1) {
-                    // batch 1: only column 8 * plane of every accumulator carries data; fetch those
+                    // batch 1: only column 8 * plane of every accumulator carries data (column `plane` in the
+                    // 16-column build, whose single core matrix holds all four planes); fetch those
                     // sixteen words with one wait instead of whole accumulators one after the other
                     uint32_t r[16];
 #pragma unroll
@@ -905,12 +906,24 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
                         for (int pl = 0; pl < 4; ++pl) {
                             r[a * 4 + pl] = 0u;
                             if (a < NACC && ((used >> a) & 1u))
-                                r[a * 4 + pl] = tmem_ld1(tlane + static_cast<uint32_t>((q * NACC + a) * NMMA + 8 * pl));
+                                r[a * 4 + pl] = tmem_ld1(tlane + static_cast<uint32_t>((q * NACC + a) * NMMA + (NMMA == 16 ? 1 : 8) * pl));
                         }
                     }
                     tmem_wait_ld(r);
 #pragma unroll
                     for (int e = 0; e < 16; ++e) v[0] += acc_from_bits<Acc>(r[e]);
+                } else if (Pol::kIsF8 && !Pol::kIsInt && NMMA == 16) {
+                    // 16-column build at batch 2: the planes are packed densely, column 2 * plane + row
+#pragma unroll
+                    for (int a = 0; a < NACC; ++a) {
+                        if ((used >> a) & 1u) {
+                            uint32_t r[16];
+                            tmem_ld16(tlane + static_cast<uint32_t>((q * NACC + a) * NMMA), r);
+                            tmem_wait_ld(r);
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) v[e & 1] += acc_from_bits<Acc>(r[e]);
+                        }
+                    }
                 } else {
 #pragma unroll
                     for (int a = 0; a < NACC; ++a) {
@@ -1605,7 +1618,7 @@ inline int launch_umma_ops(const UmmaParams *ops, int n_ops, unsigned *sync, int
     if constexpr (Pol::kIsF8 && !kChain && !Pol::kFast) {  // tensor-parallel epilogue: its own instantiation, nothing of it in the plain kernel
         if (tp_variant) kernel = umma_kernel<Pol, NMMA, kChain, true>;
     }
-    if constexpr (Pol::kIsF8 && !Pol::kIsInt && !kChain && NMMA == 32 && !Pol::kFast) {
+    if constexpr (Pol::kIsF8 && !Pol::kIsInt && !kChain && NMMA == 16 && !Pol::kFast) {
         if (ops[0].M <= 2) {
             split = true;
             kernel = umma_kernel<Pol, NMMA, kChain, false, true>;
@@ -1729,6 +1742,9 @@ inline int launch_umma(bool f8, const UmmaParams &p, int num_sms, bool pdl, cuda
         return launch_umma_one<PolF8Fast, 128>(p, num_sms, pdl, stream);
     }
     if (f8) {
+        // up to two batch rows all four planes fit one 8-row core matrix: 16 MMA columns instead of 32 halve
+        // what the tensor core reads from shared memory per MMA (the build with four TMA producers)
+        if (p.M <= 2) return launch_umma_one<PolF8, 16>(p, num_sms, pdl, stream);
         if (p.M <= 8) return launch_umma_one<PolF8, 32>(p, num_sms, pdl, stream);
         if (p.M <= 16) return launch_umma_one<PolF8, 64>(p, num_sms, pdl, stream);
         return launch_umma_one<PolF8, 128>(p, num_sms, pdl, stream);

@@ -31,9 +31,9 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 # DRAM bytes moved per algorithmic byte by the dominant kernel, from one ncu capture (see
-# profiles/umma_f8_57344x8192_b1.md): dram__bytes_read.sum + dram__bytes_write.sum = 123.48 MB
+# profiles/umma_f8_57344x8192_b1.md): dram__bytes_read.sum + dram__bytes_write.sum = 122.00 MB
 # for 117.68 MB of codes, activations, output and codebook.
-NCU_TRAFFIC_PER_ALG_BYTE = 123.48 / 117.68
+NCU_TRAFFIC_PER_ALG_BYTE = 122.00 / 117.68
 METRIC = "compressed_weight_hbm_gbs"
 UNIT = "GB/s"
 
@@ -282,7 +282,7 @@ def batch_tensor_line(dmm, torch, peaks, batch, sampler_index):
     return {"shape": [28672, 8192], "batch": batch, "us": r["us"], "tflops": r["tflops"],
             "frac_of_bf16_burst": round(r["tflops"] / burst, 4), "peak_bf16_burst": burst,
             "frac_of_2250": round(r["tflops"] / 2250.0, 4), "gbs": r["gbs"],
-            "kernel": "umma_kernel<PolF8,32>" if batch <= 8 else "umma_kernel<PolF8,64>" if batch <= 16 else "dmm_kernel<PolF8,128>",
+            "kernel": ("umma_kernel<PolF8,16>" if batch <= 2 else "umma_kernel<PolF8,32>") if batch <= 8 else "umma_kernel<PolF8,64>" if batch <= 16 else "dmm_kernel<PolF8,128>",
             "launches": r["launches"], "clocks": clocks}
 
 # ------------------------------------------------------------------------------------------
@@ -477,9 +477,9 @@ def run_ours(args):
                 "traffic": NCU_TRAFFIC_PER_ALG_BYTE * alg / n_launch if B <= 8 else None,
                 "traffic_unit": "bytes per launch (mean over the stack's launches)",
                 "traffic_source": "ncu capture of the 57344x8192 launch (profiles/umma_f8_57344x8192_b1.md): "
-                                  "123.48 MB DRAM read+write for 117.68 MB algorithmic; scaled by algorithmic bytes",
+                                  "122.00 MB DRAM read+write for 117.68 MB algorithmic; scaled by algorithmic bytes",
                 "algorithmic_bytes_per_launch": alg / n_launch,
-                "kernel": ("umma_kernel<PolF8,32,chain> (8 products per launch)" if chained else "umma_kernel<PolF8,32>") if B <= 8 else ("umma_kernel<PolF8,64>" if B <= 16 else "dmm_kernel<PolF8,128>"),
+                "kernel": ("umma_kernel<PolF8,32,chain> (8 products per launch)" if chained else ("umma_kernel<PolF8,16>" if B <= 2 else "umma_kernel<PolF8,32>")) if B <= 8 else ("umma_kernel<PolF8,64>" if B <= 16 else "dmm_kernel<PolF8,128>"),
                 "how": "all matmul launches of the stack back to back in one CUDA graph, CUDA events; per-GPU figure"
                        + ("; achieved and traffic are per product (a chained launch runs 8 products)" if chained else ""),
                 "ms": ms_kernels,

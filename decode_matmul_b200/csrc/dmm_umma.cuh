@@ -10,7 +10,8 @@
 //           value q/8: exact, and produced by the table XOR alone, 7 instructions per code),
 //           the fp16 activations split EXACTLY into four E5M2 planes (the top byte of the half,
 //           then of the remainder, ...), kind::f8f6f4, K = 32.  The planes are stacked along
-//           the MMA n dimension (N = 32 / 64 / 128 columns for up to 8 / 16 / 32 batch rows), so
+//           the MMA n dimension (N = 16 / 32 / 64 / 128 columns for up to 4 / 8 / 16 / 32 batch
+//           rows; up to 4 rows the densely packed planes are at most 16 operand rows), so
 //           one MMA per k-tile does all of them and the epilogue adds the four column groups.
 //           Up to 3 batch rows the loader warps split the activations themselves; from 4 rows
 //           on planes_kernel splits them once per call and the loaders only issue bulk copies.
@@ -18,9 +19,12 @@
 //           int8 activations as they are, kind::i8 into int32 accumulators, N = 16 / 32.
 //   PolF16  fp16 family, fp16 operands (DMM_PATH_TCGEN05): weights as fp16 integers q (byte ->
 //           half by magic number), activations as fp16, kind::f16, K = 16.  A cross-check.
+//   PolF8Fast / PolI8Fast: the same over codes in the layout of fast_decode_matmul_cuda.
 // Template flags: kChain (several dependent products in one cooperative launch, the CTAs stay
-// resident) and kTp (tensor-parallel epilogue that adds into every rank's buffer).
-// Companions in this file: planes_kernel, xrank_barrier_kernel, xrank_allreduce_kernel.
+// resident), kTp (tensor-parallel forms: epilogue that adds into every rank's buffer, producer
+// and consumer of the slots form) and kSplit (four TMA producer warps, batch 1 and 2).
+// Companions in this file: planes_kernel, xrank_barrier_kernel, xrank_allreduce_kernel,
+// tp_finalize_kernel.  Batch 17..32 of the fp16 family runs on dmm_kernel (dmm_tc.cuh).
 //
 // Work decomposition.  A super-tile is 16 strips = 256 output rows = two M=128 MMA tiles:
 // tile 0 holds strip rows 0..7 (h = 0) and tile 1 strip rows 8..15 (h = 1) of the 16 strips,
@@ -29,7 +33,7 @@
 // numbered super-tile-major and split evenly and contiguously over the CTAs (stream-K); the
 // part of a super-tile a CTA owns is a segment.
 //
-// Warp roles (25 warps):
+// Warp roles (25 warps; 28 with kSplit):
 //   0..15  decoders, four groups of four warps.  Group q takes the chunks whose CTA-wide number
 //          is q mod 4 (C k-tiles of 16 strips each).  Warp wq of a group owns TMEM lanes
 //          32wq..32wq+31 = strips 4wq..4wq+3; it reads its strips from the group's code ring,
@@ -43,7 +47,7 @@
 //          fp16 policy: warps 20 and 21 stage the chunks with cp.async).  They are the only
 //          warps that wait for the previous kernel of the stream.
 //   24     TMA producer (one thread): streams the code chunks into the groups' rings, one
-//          tiled bulk-tensor load per chunk.
+//          tiled bulk-tensor load per chunk (kSplit: warps 24..27, one per decoder group).
 // Every wait is bounded (mbar_wait); nothing spins on another CTA.
 #pragma once
 #include <cuda.h>
@@ -913,15 +917,23 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
 #pragma unroll
                     for (int e = 0; e < 16; ++e) v[0] += acc_from_bits<Acc>(r[e]);
                 } else if (Pol::kIsF8 && !Pol::kIsInt && NMMA == 16) {
-                    // 16-column build at batch 2: the planes are packed densely, column 2 * plane + row
+                    // 16-column build at batch 2 .. 4: the planes are packed densely, column M * plane + row
 #pragma unroll
                     for (int a = 0; a < NACC; ++a) {
                         if ((used >> a) & 1u) {
                             uint32_t r[16];
                             tmem_ld16(tlane + static_cast<uint32_t>((q * NACC + a) * NMMA), r);
                             tmem_wait_ld(r);
+                            if (p.M == 2) {
 #pragma unroll
-                            for (int e = 0; e < 8; ++e) v[e & 1] += acc_from_bits<Acc>(r[e]);
+                                for (int e = 0; e < 8; ++e) v[e & 1] += acc_from_bits<Acc>(r[e]);
+                            } else if (p.M == 3) {
+#pragma unroll
+                                for (int e = 0; e < 12; ++e) v[e % 3] += acc_from_bits<Acc>(r[e]);
+                            } else {
+#pragma unroll
+                                for (int e = 0; e < 16; ++e) v[e & 3] += acc_from_bits<Acc>(r[e]);
+                            }
                         }
                     }
                 } else {
@@ -1119,7 +1131,8 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
             const int E0 = first_epoch_tiles(E, static_cast<int>(p.M));           // the first one is short
             // fp8: a plane is one 8-row core matrix (rows past the batch overlap the next plane and
             // land in unused columns) or, for the 16-row layout, two of them
-            const uint64_t xdesc0 = Pol::kIsF8 ? smem_desc(x_addr, tile_b / 2, (NMMA > 32 || Pol::kIsInt) ? 128u : tile_b / 8)
+            // (16 columns: the two core matrices are 16 consecutive rows of the densely packed planes)
+            const uint64_t xdesc0 = Pol::kIsF8 ? smem_desc(x_addr, tile_b / 2, (NMMA > 32 || NMMA == 16 || Pol::kIsInt) ? 128u : tile_b / 8)
                                                : smem_desc(x_addr, NMMA * 16, 128);
             int cur_ep = -1, ep_beg = 0, ep_end = 0;  // fp8: epoch of this op being read and its k-tile range
             int ep_slot = eg_base % Plan::kEpochs;    // its buffer, the parity of that buffer's barriers
@@ -1742,9 +1755,10 @@ inline int launch_umma(bool f8, const UmmaParams &p, int num_sms, bool pdl, cuda
         return launch_umma_one<PolF8Fast, 128>(p, num_sms, pdl, stream);
     }
     if (f8) {
-        // up to two batch rows all four planes fit one 8-row core matrix: 16 MMA columns instead of 32 halve
-        // what the tensor core reads from shared memory per MMA (the build with four TMA producers)
-        if (p.M <= 2) return launch_umma_one<PolF8, 16>(p, num_sms, pdl, stream);
+        // up to four batch rows the four planes, packed densely, are at most 16 rows of the operand (up to two
+        // rows they fit ONE 8-row core matrix): 16 MMA columns instead of 32 halve what the tensor core reads
+        // from shared memory per MMA (up to two rows: the build with four TMA producers)
+        if (p.M <= 4) return launch_umma_one<PolF8, 16>(p, num_sms, pdl, stream);
         if (p.M <= 8) return launch_umma_one<PolF8, 32>(p, num_sms, pdl, stream);
         if (p.M <= 16) return launch_umma_one<PolF8, 64>(p, num_sms, pdl, stream);
         return launch_umma_one<PolF8, 128>(p, num_sms, pdl, stream);

@@ -10,8 +10,8 @@
 //           value q/8: exact, and produced by the table XOR alone, 7 instructions per code),
 //           the fp16 activations split EXACTLY into four E5M2 planes (the top byte of the half,
 //           then of the remainder, ...), kind::f8f6f4, K = 32.  The planes are stacked along
-//           the MMA n dimension (N = 16 / 32 / 64 / 128 columns for up to 4 / 8 / 16 / 32 batch
-//           rows; up to 4 rows the densely packed planes are at most 16 operand rows), so
+//           the MMA n dimension (N = 16 / 32 / 64 / 128 columns for up to 2 / 8 / 16 / 32 batch
+//           rows; up to 2 rows the densely packed planes fit one 8-row core matrix), so
 //           one MMA per k-tile does all of them and the epilogue adds the four column groups.
 //           Up to 3 batch rows the loader warps split the activations themselves; from 4 rows
 //           on planes_kernel splits them once per call and the loaders only issue bulk copies.
@@ -249,8 +249,9 @@ constexpr int kMaxEpoch = 48;    // and at most this many in the later ones: sho
                                  // loaders' latency per epoch below the time the previous one lasts
 
 // k-tiles of the first epoch: one 16-byte piece per thread of a loader team (4 * M pieces per tile)
-__host__ __device__ inline int first_epoch_tiles(int E, int M) {
-    int e0 = (kFirstEpoch / M) & ~1;
+__host__ __device__ inline int first_epoch_tiles(int E, int M, int ntiles) {
+    // (batch 1 with a long tile sequence: 8 measured better than 16, 4 and 2; short sequences: one epoch of 16)
+    int e0 = (M == 1 && ntiles >= 64) ? kFirstEpoch / 2 : (kFirstEpoch / M) & ~1;
     if (e0 < 2) e0 = 2;
     return e0 < E ? e0 : E;
 }
@@ -917,23 +918,15 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
 #pragma unroll
                     for (int e = 0; e < 16; ++e) v[0] += acc_from_bits<Acc>(r[e]);
                 } else if (Pol::kIsF8 && !Pol::kIsInt && NMMA == 16) {
-                    // 16-column build at batch 2 .. 4: the planes are packed densely, column M * plane + row
+                    // 16-column build at batch 2: the planes are packed densely, column 2 * plane + row
 #pragma unroll
                     for (int a = 0; a < NACC; ++a) {
                         if ((used >> a) & 1u) {
                             uint32_t r[16];
                             tmem_ld16(tlane + static_cast<uint32_t>((q * NACC + a) * NMMA), r);
                             tmem_wait_ld(r);
-                            if (p.M == 2) {
 #pragma unroll
-                                for (int e = 0; e < 8; ++e) v[e & 1] += acc_from_bits<Acc>(r[e]);
-                            } else if (p.M == 3) {
-#pragma unroll
-                                for (int e = 0; e < 12; ++e) v[e % 3] += acc_from_bits<Acc>(r[e]);
-                            } else {
-#pragma unroll
-                                for (int e = 0; e < 16; ++e) v[e & 3] += acc_from_bits<Acc>(r[e]);
-                            }
+                            for (int e = 0; e < 8; ++e) v[e & 1] += acc_from_bits<Acc>(r[e]);
                         }
                     }
                 } else {
@@ -1128,11 +1121,10 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
             // descriptor of activation stage 0; later stages and k-halves only move the address field
             const uint32_t tile_b = plane_tile_bytes<NMMA, Pol::kIsInt != 0>(static_cast<int>(p.M));  // fp8: bytes of one k-tile of planes
             const int E = epoch_tiles(Plan::kEpochBytes, tile_b);  // k-tiles per epoch
-            const int E0 = first_epoch_tiles(E, static_cast<int>(p.M));           // the first one is short
+            const int E0 = first_epoch_tiles(E, static_cast<int>(p.M), i1 - i0);  // the first one is short
             // fp8: a plane is one 8-row core matrix (rows past the batch overlap the next plane and
             // land in unused columns) or, for the 16-row layout, two of them
-            // (16 columns: the two core matrices are 16 consecutive rows of the densely packed planes)
-            const uint64_t xdesc0 = Pol::kIsF8 ? smem_desc(x_addr, tile_b / 2, (NMMA > 32 || NMMA == 16 || Pol::kIsInt) ? 128u : tile_b / 8)
+            const uint64_t xdesc0 = Pol::kIsF8 ? smem_desc(x_addr, tile_b / 2, (NMMA > 32 || Pol::kIsInt) ? 128u : tile_b / 8)
                                                : smem_desc(x_addr, NMMA * 16, 128);
             int cur_ep = -1, ep_beg = 0, ep_end = 0;  // fp8: epoch of this op being read and its k-tile range
             int ep_slot = eg_base % Plan::kEpochs;    // its buffer, the parity of that buffer's barriers
@@ -1356,12 +1348,17 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
             grid_dep_launch();
             tp_slots_now = p.peer_out[p.tp_rank] + static_cast<long long>(e & 1u) * p.tp_world * p.tp_count;
         }
-        if (p.zero_ptr != nullptr) {  // a later kernel or op will accumulate into it
-            constexpr int ZT = kULoadWarps * 32;
-            for (long long i = static_cast<long long>(cta) * ZT + wl * 32 + lane; i < p.zero_count;
-                 i += static_cast<long long>(gridDim.x) * ZT)
-                p.zero_ptr[i] = 0.f;
-        }
+        // a later kernel or op will accumulate into zero_ptr: clear it on the way -- in a chain before this
+        // CTA's arrival for the op, otherwise after the activations are staged (nothing waits for it)
+        auto clear_zero = [&]() {
+            if (p.zero_ptr != nullptr) {
+                constexpr int ZT = kULoadWarps * 32;
+                for (long long i = static_cast<long long>(cta) * ZT + wl * 32 + lane; i < p.zero_count;
+                     i += static_cast<long long>(gridDim.x) * ZT)
+                    p.zero_ptr[i] = 0.f;
+            }
+        };
+        if (n_ops > 1) clear_zero();
         if (kTp && p.tp_mode == 2) {
             // producer of epoch e + 1 (counter = e now that the previous kernel has finished): this rank's own
             // slot of parity e & 1 was read for the last time by the consumer before this kernel; clear it
@@ -1403,7 +1400,7 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
             const int E = epoch_tiles(Plan::kEpochBytes, tile_b);
             // The first epoch is short: nothing can be multiplied before it is staged, and the
             // loaders may only start once the previous kernel of the stream has finished.
-            const int E0 = first_epoch_tiles(E, M);
+            const int E0 = first_epoch_tiles(E, M, i1 - i0);
             const int ntiles = i1 - i0;
             const int nep = ntiles <= 0 ? 0 : (ntiles <= E0 ? 1 : 1 + (ntiles - E0 + E - 1) / E);
             // two teams of loader warps fill alternate epochs, so that the global-memory latency
@@ -1554,6 +1551,7 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
                 retire();
             }
         }
+        if (n_ops == 1) clear_zero();
         }  // op
     }
 
@@ -1755,10 +1753,10 @@ inline int launch_umma(bool f8, const UmmaParams &p, int num_sms, bool pdl, cuda
         return launch_umma_one<PolF8Fast, 128>(p, num_sms, pdl, stream);
     }
     if (f8) {
-        // up to four batch rows the four planes, packed densely, are at most 16 rows of the operand (up to two
-        // rows they fit ONE 8-row core matrix): 16 MMA columns instead of 32 halve what the tensor core reads
-        // from shared memory per MMA (up to two rows: the build with four TMA producers)
-        if (p.M <= 4) return launch_umma_one<PolF8, 16>(p, num_sms, pdl, stream);
+        // up to two batch rows all four planes fit one 8-row core matrix: 16 MMA columns instead of 32 halve
+        // what the tensor core reads from shared memory per MMA (the build with four TMA producers).  For 3
+        // and 4 rows (two core matrices of the dense planes) it measured 1-2 % faster but cost batch 2 3 %.
+        if (p.M <= 2) return launch_umma_one<PolF8, 16>(p, num_sms, pdl, stream);
         if (p.M <= 8) return launch_umma_one<PolF8, 32>(p, num_sms, pdl, stream);
         if (p.M <= 16) return launch_umma_one<PolF8, 64>(p, num_sms, pdl, stream);
         return launch_umma_one<PolF8, 128>(p, num_sms, pdl, stream);

@@ -53,6 +53,8 @@
 #include <cuda.h>
 
 #include <atomic>
+#include <functional>
+#include <unordered_map>
 #include "dmm_common.cuh"
 #include "dmm_launch.h"
 
@@ -1601,6 +1603,27 @@ inline EncodeTiledFn encode_tiled_fn() {
 // With `fast` the matrix is in the layout of fast_decode_matmul_cuda, seen as uint32 [row blocks of 32][K/16 * 32]:
 // a k-tile of a row block is 64 consecutive words, box = c_tiles k-tiles x 8 row blocks (the same 8 KiB).
 inline int make_codes_map(CUtensorMap *map, const void *codes, long long N, long long K, int c_tiles, bool fast = false) {
+    // A model calls with the same weight matrices over and over: the maps a host thread has encoded are kept
+    // (a map depends on nothing but these arguments, so a recycled address gives the same map).
+    struct Key {
+        const void *codes;
+        long long N, K;
+        int c_tiles, fast;
+        bool operator==(const Key &o) const { return codes == o.codes && N == o.N && K == o.K && c_tiles == o.c_tiles && fast == o.fast; }
+    };
+    struct KeyHash {
+        size_t operator()(const Key &k) const {
+            return std::hash<const void *>()(k.codes) ^ (static_cast<size_t>(k.N) * 0x9E3779B97F4A7C15ull) ^ (static_cast<size_t>(k.K) << 20) ^
+                   static_cast<size_t>(k.c_tiles * 2 + k.fast);
+        }
+    };
+    thread_local std::unordered_map<Key, CUtensorMap, KeyHash> cache;
+    const Key key{codes, N, K, c_tiles, fast ? 1 : 0};
+    const auto hit = cache.find(key);
+    if (hit != cache.end()) {
+        *map = hit->second;
+        return 0;
+    }
     EncodeTiledFn fn = encode_tiled_fn();
     if (fn == nullptr) return cudaErrorNotSupported;
     const cuuint64_t gdim[2] = {static_cast<cuuint64_t>(fast ? 2 * K : K), static_cast<cuuint64_t>(fast ? N / 32 : N / 16)};
@@ -1610,7 +1633,10 @@ inline int make_codes_map(CUtensorMap *map, const void *codes, long long N, long
     const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 2, const_cast<void *>(codes), gdim, gstride, box, estride,
                           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? 0 : cudaErrorInvalidValue;
+    if (r != CUDA_SUCCESS) return cudaErrorInvalidValue;
+    if (cache.size() >= 8192) cache.clear();  // (bounded: a process that streams ever new matrices just re-encodes)
+    cache.emplace(key, *map);
+    return 0;
 }
 
 template <class Pol, int NMMA, bool kChain>

@@ -284,7 +284,12 @@ struct UmmaPlan {
     // group are issued by different warps (each accumulator still has exactly one issuer, so the
     // summation order stays fixed)
     static constexpr int kTileParts = kNAcc <= 2 ? 2 : 1;
-    static constexpr uint32_t kDCols = 2 * kNAcc * NMMA;          // TMEM: accumulators first
+    // accumulator sets: with 16 MMA columns two sets fit next to the weight slots, and the segments of a CTA
+    // (the parts of different super-tiles in its tile range) alternate between them, so that the epilogue of
+    // one segment runs while the MMAs of the next are already being issued
+    static constexpr int kSets = (Pol::kIsF8 && !Pol::kIsInt && NMMA == 16) ? 2 : 1;
+    static constexpr uint32_t kSetCols = 2 * kNAcc * NMMA;        // one set: both MMA tiles of every accumulator
+    static constexpr uint32_t kDCols = kSetCols * kSets;          // TMEM: accumulators first
     static constexpr uint32_t kBufCols = 2 * Pol::kG * Pol::kACols;  // one group buffer: [tile][k-tile][cols]
     static constexpr uint32_t kACols = 4 * kNA * kBufCols;
     static_assert(kDCols + kACols <= kUTmemCols, "TMEM plan exceeds 512 columns");
@@ -313,8 +318,8 @@ struct UmmaPlan {
     static constexpr int kBarXReady = kBarFree + kSlots;                 // [kEpochs] loader warps
     static constexpr int kBarXFree = kBarXReady + kEpochs;               // [kEpochs] both issuers (commit)
     static constexpr int kBarDReady = kBarXFree + kEpochs;
-    static constexpr int kBarDFree = kBarDReady + 1;
-    static constexpr int kBarGridOk = kBarDFree + 1;  // chains: this CTA's loaders have seen the previous op complete
+    static constexpr int kBarDFree = kBarDReady + kSets;  // [kSets] each, one per accumulator set
+    static constexpr int kBarGridOk = kBarDFree + kSets;  // chains: this CTA's loaders have seen the previous op complete
     static constexpr int kBarCount = kBarGridOk + 1;
     static_assert(kBarCount * 8 + 64 <= kUBarBytes, "barrier block too small");
 };
@@ -744,8 +749,8 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
             if (bt >= Plan::kBarXReady && bt < Plan::kBarXFree) count = p0.x_planes != nullptr ? 1 : kULoadWarps / kULoadTeams;
             if (bt >= Plan::kBarFree && bt < Plan::kBarXReady) count = TP;  // tcgen05.commit of every issuer of the slot
             if (bt >= Plan::kBarXFree && bt < Plan::kBarDReady) count = NACC * TP;
-            if (bt == Plan::kBarDReady) count = NACC * TP;
-            if (bt == Plan::kBarDFree) count = 8;
+            if (bt >= Plan::kBarDReady && bt < Plan::kBarDFree) count = NACC * TP;
+            if (bt >= Plan::kBarDFree && bt < Plan::kBarGridOk) count = 8;
             if (bt == Plan::kBarGridOk) count = kULoadWarps;
             mbar_init(bar(bt), count);
             if (bt == 0) {
@@ -888,7 +893,9 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
                 // accumulator a was written in this segment iff one of its chunks has parity a
                 uint32_t used = 0;
                 for (int cc = 0; cc < nchunks && cc < NACC; ++cc) used |= 1u << ((ebase + cc) % NACC);
-                mbar_wait(bar(Plan::kBarDReady), static_cast<uint32_t>(segidx & 1), flags);
+                const int aset = segidx % Plan::kSets;  // accumulator set of this segment
+                const uint32_t aset_col = static_cast<uint32_t>(aset) * Plan::kSetCols;
+                mbar_wait(bar(Plan::kBarDReady + aset), static_cast<uint32_t>((segidx / Plan::kSets) & 1), flags);
                 tc_fence_after();
                 // the accumulators are fp32, or int32 for the integer family (exact, no scale)
                 using Acc = typename AccType<Pol::kIsInt != 0>::type;
@@ -913,7 +920,7 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
                         for (int pl = 0; pl < 4; ++pl) {
                             r[a * 4 + pl] = 0u;
                             if (a < NACC && ((used >> a) & 1u))
-                                r[a * 4 + pl] = tmem_ld1(tlane + static_cast<uint32_t>((q * NACC + a) * NMMA + (NMMA == 16 ? 1 : 8) * pl));
+                                r[a * 4 + pl] = tmem_ld1(tlane + aset_col + static_cast<uint32_t>((q * NACC + a) * NMMA + (NMMA == 16 ? 1 : 8) * pl));
                         }
                     }
                     tmem_wait_ld(r);
@@ -925,7 +932,7 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
                     for (int a = 0; a < NACC; ++a) {
                         if ((used >> a) & 1u) {
                             uint32_t r[16];
-                            tmem_ld16(tlane + static_cast<uint32_t>((q * NACC + a) * NMMA), r);
+                            tmem_ld16(tlane + aset_col + static_cast<uint32_t>((q * NACC + a) * NMMA), r);
                             tmem_wait_ld(r);
 #pragma unroll
                             for (int e = 0; e < 8; ++e) v[e & 1] += acc_from_bits<Acc>(r[e]);
@@ -938,7 +945,7 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
 #pragma unroll
                             for (int b0 = 0; b0 < NMMA; b0 += 16) {
                                 uint32_t r[16];
-                                tmem_ld16(tlane + static_cast<uint32_t>((q * NACC + a) * NMMA + b0), r);
+                                tmem_ld16(tlane + aset_col + static_cast<uint32_t>((q * NACC + a) * NMMA + b0), r);
                                 tmem_wait_ld(r);
                                 // PolF8: column 8*plane + b; PolF16: column b
 #pragma unroll
@@ -949,7 +956,7 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
                 }
                 tc_fence_before();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(bar(Plan::kBarDFree));
+                if (lane == 0) mbar_arrive(bar(Plan::kBarDFree + aset));
 
                 const int ss_a = ss * KT;
                 const bool full = len == KT;
@@ -1138,10 +1145,12 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
             for (int ss = ss_first; ss <= ss_last; cbase += seg_chunks(ss), jseg += seg_len(ss), ++ss, ++segidx) {
                 const int len = seg_len(ss);
                 const int nchunks = (len + C - 1) / C;
-                if (segidx > 0) {
-                    mbar_wait(bar(Plan::kBarDFree), static_cast<uint32_t>((segidx - 1) & 1), flags);
+                const int aset = segidx % Plan::kSets;  // accumulator set of this segment
+                if (segidx >= Plan::kSets) {  // the epilogue has read what the set held before
+                    mbar_wait(bar(Plan::kBarDFree + aset), static_cast<uint32_t>(((segidx / Plan::kSets) - 1) & 1), flags);
                     tc_fence_after();
                 }
+                [[maybe_unused]] const uint32_t d_seg = d_col0 + static_cast<uint32_t>(aset) * Plan::kSetCols;
                 bool first = true;  // the accumulators hold nothing of this segment yet
                 for (int c = (me - cbase) & (NACC - 1); c < nchunks; c += NACC) {
                     const int q = (cbase + c) & 3;
@@ -1184,10 +1193,10 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
                                     const uint32_t acc = (first && i == 0) ? 0u : 1u;
                                     if (leader) {
                                         if constexpr (TP == 1) {
-                                            mma_ts_f8_lh<Pol::kIsInt != 0>(d_col0, a_col + i * Pol::kACols, xlo, xdesc_hi, idesc, acc);
-                                            mma_ts_f8_lh<Pol::kIsInt != 0>(d_col0 + NACC * NMMA, a_col + (G + i) * Pol::kACols, xlo, xdesc_hi, idesc, acc);
+                                            mma_ts_f8_lh<Pol::kIsInt != 0>(d_seg, a_col + i * Pol::kACols, xlo, xdesc_hi, idesc, acc);
+                                            mma_ts_f8_lh<Pol::kIsInt != 0>(d_seg + NACC * NMMA, a_col + (G + i) * Pol::kACols, xlo, xdesc_hi, idesc, acc);
                                         } else {
-                                            mma_ts_f8_lh<Pol::kIsInt != 0>(d_col0, a_col + (tp * G + i) * Pol::kACols, xlo, xdesc_hi, idesc, acc);
+                                            mma_ts_f8_lh<Pol::kIsInt != 0>(d_seg, a_col + (tp * G + i) * Pol::kACols, xlo, xdesc_hi, idesc, acc);
                                         }
                                     }
                                 }
@@ -1209,7 +1218,7 @@ __global__ void __launch_bounds__(kSplit ? kUThreads : kUThreads - (kUTmaWarps -
                     }
                     if (q == 0) cnt0 = cn; else if (q == 1) cnt1 = cn; else if (q == 2) cnt2 = cn; else cnt3 = cn;
                 }
-                if (leader) tc_commit(bar(Plan::kBarDReady));
+                if (leader) tc_commit(bar(Plan::kBarDReady + aset));
             }
             if constexpr (Pol::kIsF8) {
                 const int nep = i1 <= i0 ? 0 : (i1 - i0 <= E0 ? 1 : 1 + (i1 - i0 - E0 + E - 1) / E);

@@ -331,7 +331,7 @@ class LinearStack:
             if peer is not None:
                 # The slots form (no cross-rank kernel, no barrier) is the fastest at every rank count measured on
                 # B200 at batch 1 (ms per step of the Llama-2-70B stack at 2 / 4 / 8 ranks: slots 5.11 / 4.03 / 3.81,
-                # push 5.55 / 4.83 / 4.97, pull 5.43 / 5.06 / 5.97); it splits the activations inside the kernel, so larger batches take the
+                # push 5.22 / 4.83 / 4.97, pull 5.16 / 5.06 / 5.97); it splits the activations inside the kernel, so larger batches take the
                 # one-shot all-reduce kernel (few ranks) or the epilogues that add into every rank (many ranks).
                 default = "slots" if h.shape[0] <= 8 else ("pull" if self.world <= 2 else "push")
                 mode = self.tp_mode or os.environ.get("DMM_TP_MODE", default)
